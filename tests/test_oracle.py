@@ -1,0 +1,174 @@
+"""The CPU oracle against the committed fixtures and against first principles."""
+import json
+import os
+from fractions import Fraction
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import paro_oracle as po
+
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def test_perm_index_matches_reference_cogvideox():
+    ref = torch.from_numpy(np.load(os.path.join(GOLD, "perm_cogvideox_ref.npz"))["table"])
+    n_text = 226
+    assert torch.equal(ref[:, :n_text], torch.arange(n_text, dtype=torch.int32).expand(6, -1))
+    mine = po.perm_index_table(range(6), (13, 30, 45)) + n_text
+    assert torch.equal(ref[:, n_text:], mine)
+
+
+def test_perm_index_matches_reference_wan():
+    with open(os.path.join(GOLD, "perm_wan_ref_sha256.json")) as f:
+        g = json.load(f)
+    mine = po.perm_index_table(range(6), tuple(g["grid"]))
+    assert po.sha256_of(mine) == g["sha256_int32_table_6xN"]
+    assert mine[:, :8].tolist() == g["first8"] and mine[:, -8:].tolist() == g["last8"]
+
+
+@pytest.mark.parametrize("grid,n_text", [((2, 3, 4), 0), ((3, 4, 5), 7)])
+def test_permute_roundtrip(grid, n_text):
+    n = n_text + grid[0] * grid[1] * grid[2]
+    x = torch.randn(2, 6, n, 4)
+    y = po.permute_tokens(x, range(6), grid, n_text)
+    assert torch.equal(po.inverse_permute_tokens(y, range(6), grid, n_text), x)
+    assert torch.equal(y[:, :, :n_text], x[:, :, :n_text])
+    assert torch.equal(y[:, 0], x[:, 0])
+
+
+def test_kat_ramp_fixture_and_exact_rational():
+    g = np.load(os.path.join(GOLD, "kat_ramp_int8.npz"))
+    rows = torch.arange(-256, 256, dtype=torch.bfloat16).unsqueeze(1).repeat(1, 64).reshape(1, 1, 512, 64)
+    q8, qs = po.quant_int8(rows, 32)
+    k8, ks = po.quant_int8(rows, 64)
+    assert np.array_equal(q8[0, 0, :, 0].numpy(), g["q_col0"]) and np.array_equal(qs.numpy(), g["q_scale"])
+    assert np.array_equal(k8[0, 0, :, 0].numpy(), g["k_col0"]) and np.array_equal(ks.numpy(), g["k_scale"])
+    # exact rational arithmetic agrees to within one code (fp32 products may sit on the other
+    # side of a rounding boundary) and exactly at the block extremes
+    vals = list(range(-256, 256))
+    for grp, q in ((32, q8), (64, k8)):
+        for b0 in range(0, 512, grp):
+            amax = max(abs(v) for v in vals[b0:b0 + grp])
+            for r in range(b0, b0 + grp):
+                exact = Fraction(vals[r] * 127, amax)
+                assert abs(int(q[0, 0, r, 0]) - exact) <= Fraction(1, 2) + Fraction(1, 1000)
+            assert max(abs(int(q[0, 0, r, 0])) for r in range(b0, b0 + grp)) == 127
+    assert torch.equal(qs.flatten()[:1], torch.tensor([256.0]) / 127.0)
+
+
+def test_quant_int8_tail_and_smoothing():
+    g = torch.Generator().manual_seed(1)
+    x = (torch.randn(1, 2, 100, 64, generator=g) + 3.0).to(torch.bfloat16)
+    km = po.channel_mean(x, x.dtype)
+    q, s = po.quant_int8(x, 64, km=km)
+    assert q.shape == x.shape and s.shape == (1, 2, 2)
+    deq = q.float() * s.repeat_interleave(64, dim=-1)[:, :, :100].unsqueeze(-1) + km.float().unsqueeze(2)
+    assert (deq - x.float()).abs().max() <= s.max() * 0.5 + 1e-6
+    q32, s32 = po.quant_int8(x, 32)
+    assert s32.shape == (1, 2, 4)
+    q96, s96 = po.quant_int8(x[:, :, :96], 32)
+    assert s96.shape == (1, 2, 4) and s96[0, 0, 3] == torch.tensor(1e-7) / 127  # rows 96..127 all padding
+    assert torch.equal(q96, q32[:, :, :96]) and torch.equal(s96[..., :3], s32[..., :3])
+
+
+def test_quant_v_fp8_layout_and_range():
+    g = torch.Generator().manual_seed(2)
+    v = (torch.randn(1, 2, 70, 64, generator=g) * 3 + 1).to(torch.float16)
+    v8, vs, vm = po.quant_v_fp8(v, smooth=True)
+    assert v8.shape == (1, 2, 64, 128) and vs.shape == (1, 2, 64) and vm.shape == (1, 2, 64)
+    assert (v8[..., 70:].view(torch.uint8) == 0).all()
+    assert v8.float().abs().max() == 448.0
+    deq = v8[..., :70].float().transpose(2, 3) * vs.unsqueeze(2) + vm.unsqueeze(2)
+    assert ((deq - v.float()).abs() <= 0.0625 * (v.float() - vm.unsqueeze(2)).abs() + 2e-3 * vs.unsqueeze(2) * 448).all()
+    z8, zs, _ = po.quant_v_fp8(torch.zeros(1, 1, 64, 64, dtype=torch.float16), smooth=False)
+    assert torch.isfinite(z8.float()).all() and (z8.view(torch.uint8) == 0).all()
+
+
+def test_compact_and_pair_plans():
+    m = po.make_mask(3, 7, 0.4, seed=5)
+    ptr, cols = po.compact_plan(m)
+    flat = m.reshape(-1, 7)
+    for r in range(flat.shape[0]):
+        assert cols[ptr[r]:ptr[r + 1]].tolist() == flat[r].nonzero().flatten().tolist()
+    pptr, pent = po.pair_union_plan(m)
+    npairs = 4
+    assert pptr.numel() == 3 * npairs + 1
+    for s in range(3):
+        for p in range(npairs):
+            ent = pent[pptr[s * npairs + p]:pptr[s * npairs + p + 1]].tolist()
+            want = []
+            for kb in range(7):
+                f = int(m[s, 2 * p, kb]) + (2 * int(m[s, 2 * p + 1, kb]) if 2 * p + 1 < 7 else 0)
+                if f:
+                    want.append(kb * 4 + f)
+            assert ent == want
+
+
+def test_attention_dense_matches_sdpa():
+    g = torch.Generator().manual_seed(3)
+    B, H, N, D = 1, 2, 200, 64
+    q = torch.randn(B, H, N, D, generator=g).to(torch.float16)
+    k = (torch.randn(B, H, N, D, generator=g) + 1.0).to(torch.float16)
+    v = torch.randn(B, H, N, D, generator=g).to(torch.float16)
+    mask = torch.ones(H, 4, 4, dtype=torch.bool)
+    out, lse = po.paro_attention(q, k, v, [0, 0], mask, (1, 10, 20), return_lse=True)
+    ref = torch.nn.functional.scaled_dot_product_attention(q.float(), k.float(), v.float())
+    assert po.cosine_per_head(out, ref).min() > 0.999
+    s = (q.float() @ k.float().transpose(-1, -2)) * D ** -0.5
+    # K smoothing leaves O unchanged up to quantisation noise but shifts every score of a row by
+    # q.km, so the LSE is only comparable without it
+    out2, lse2 = po.paro_attention(q, k, v, [0, 0], mask, (1, 10, 20), smooth_k=False, return_lse=True)
+    assert po.cosine_per_head(out2, ref).min() > 0.995
+    assert (lse2 - torch.logsumexp(s, dim=-1)).abs().max() < 0.05
+
+
+def test_attention_permutation_invariance_when_dense():
+    """With every block kept the permutation must cancel out of the result."""
+    g = torch.Generator().manual_seed(4)
+    q, k, v, _ = po.make_inputs(1, 6, 4 * 4 * 8, 64, torch.bfloat16, seed=4)
+    mask = torch.ones(6, 2, 2, dtype=torch.bool)
+    a = po.paro_attention(q, k, v, [0] * 6, mask, (4, 4, 8))
+    b = po.paro_attention(q, k, v, list(range(6)), mask, (4, 4, 8))
+    assert po.cosine_per_head(a, b).min() > 0.9995
+
+
+def test_rope_tables_and_rotation():
+    cos, sin = po.rope_full_tables((2, 3, 4), 64, "cogvideox")
+    assert cos.shape == (24, 32) and cos.dtype == torch.float32
+    assert po.rope_axis_pairs(64, "cogvideox") == (8, 12, 12)
+    assert po.rope_axis_pairs(128, "wan") == (22, 21, 21)
+    x = torch.randn(1, 1, 5 + 24, 64).to(torch.bfloat16)
+    y = po.apply_rope_real(x, cos, sin, n_text=5)
+    assert torch.equal(y[:, :, :5], x[:, :, :5])
+    assert torch.equal(y[:, :, 5], x[:, :, 5])  # position (0,0,0): zero angle
+    n0 = x[:, :, 5:].float().reshape(1, 1, 24, 32, 2).norm(dim=-1)
+    n1 = y[:, :, 5:].float().reshape(1, 1, 24, 32, 2).norm(dim=-1)
+    assert (n0 - n1).abs().max() < 0.05
+    cw, sw = po.rope_full_tables((2, 3, 4), 128, "wan")
+    assert cw.dtype == torch.float64
+    xw = torch.randn(1, 1, 24, 128).to(torch.bfloat16)
+    yw = po.apply_rope_complex(xw, cw, sw)
+    z = torch.view_as_complex(xw.double().unflatten(3, (-1, 2))) * torch.polar(torch.ones_like(cw), torch.atan2(sw, cw))
+    assert (torch.view_as_real(z).flatten(3) - yw.double()).abs().max() < 0.02
+
+
+def test_c1_fixture():
+    with open(os.path.join(GOLD, "c1_plumbing_sha256.json")) as f:
+        g = json.load(f)
+    cfg = po.CONFIGS["c1_plumbing"]
+    N = 4 * 16 * 16
+    q, k, v, orders = po.make_inputs(cfg["B"], cfg["H"], N, cfg["D"], cfg["dtype"], seed=0)
+    assert orders == g["orders"]
+    mask = po.make_mask(cfg["H"], 16, cfg["density"], seed=0)
+    d = g["digests"]
+    assert po.sha256_of(q) == d["q"] and po.sha256_of(mask.to(torch.uint8)) == d["mask"]
+    qp = po.permute_tokens(q, orders, cfg["grid"])
+    q8, qs = po.quant_int8(qp, 32)
+    assert po.sha256_of(q8) == d["q_int8"] and po.sha256_of(qs) == d["q_scale"]
+    ptr, cols = po.compact_plan(mask)
+    assert po.sha256_of(ptr) == d["row_ptr"] and po.sha256_of(cols) == d["cols"]
+    out = po.paro_attention(q, k, v, orders, mask, cfg["grid"])
+    gold = torch.from_numpy(np.load(os.path.join(GOLD, "c1_plumbing_out.npz"))["out"]).view(torch.float16)
+    assert torch.equal(out, gold)
