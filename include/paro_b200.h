@@ -1,0 +1,148 @@
+/*
+ * paro_b200.h -- C ABI of libparo_b200.so: PAROAttention's quantized, reordered,
+ * block-sparse attention path for NVIDIA B200 (sm_100a).
+ *
+ * Conventions (they replace the torch-extension conventions of the reference,
+ * csrc/qattn/pybind_sm80.cpp:23-26, csrc/fused/pybind.cpp:23-32, csrc/rope/pybind.cpp:7):
+ *   - every pointer is a DEVICE pointer on the current device unless said otherwise;
+ *   - the caller owns every buffer, scratch included (sizes from the *_scratch_bytes calls);
+ *   - every call is asynchronous on `stream` (a cudaStream_t) and returns 0 or a negative
+ *     PARO_E* code; paro_last_error() gives the message of the calling thread's last failure;
+ *   - tensors are [B,H,N,D] addressed through element strides (stride_d == 1), so both the
+ *     reference's "HND" and "NHD" layouts are accepted (core.py:176, fused.cu:452-470);
+ *   - D is 64 or 128 (core.py:181-192), dtype is PARO_F16 or PARO_BF16 (core.py:163).
+ * There is no CPU fallback: a call made without a usable CUDA device fails with PARO_ECUDA.
+ */
+#ifndef PARO_B200_H
+#define PARO_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* paro_stream_t; /* cudaStream_t */
+
+enum {
+  PARO_OK = 0,
+  PARO_EINVAL = -1,   /* bad flag, null pointer, unsupported dtype */
+  PARO_ESHAPE = -2,   /* unsupported or inconsistent sizes */
+  PARO_EALIGN = -3,   /* pointer or stride not aligned as required */
+  PARO_ETIMEOUT = -4, /* a bounded device-side wait expired (reported through the status word) */
+  PARO_ECUDA = -5,    /* CUDA runtime / driver error */
+  PARO_ECAP = -6      /* caller-provided capacity too small */
+};
+
+enum { PARO_F16 = 0, PARO_BF16 = 1 };
+enum { PARO_ROPE_NONE = 0, PARO_ROPE_REAL_F32 = 1, PARO_ROPE_COMPLEX_F64 = 2 };
+
+int paro_version(void);
+const char* paro_last_error(void);
+
+/* ---- token permutation --------------------------------------------------------------- */
+
+/* idx[h][j] = index (within the F*Hh*W video tokens) of the token that lands at position j
+ * after head h's axis reordering; order ids 0..5 = FHW,FWH,HWF,HFW,WHF,WFH.
+ * Replaces the per-head reshape/permute of paroattention/cogvideox.py:38-56 (wan.py:40-56). */
+int paro_build_perm_index(const int32_t* order_ids, int H, int F, int Hh, int W,
+                          int32_t* idx, paro_stream_t stream);
+
+/* Fused 3D-RoPE + per-head token permutation of ONE tensor, out-of-place.
+ *   forward (inverse=0): out[b,h,n_text+j,:] = rope(in[b,h,n_text+idx_h[j],:]); text rows copied;
+ *   inverse (inverse=1): out[b,h,n_text+idx_h[j],:] = in[b,h,n_text+j,:] (rope_mode must be NONE).
+ * order_ids == NULL means no permutation (RoPE only).  `out` is contiguous [B,H,N,D].
+ * cos_tab/sin_tab: [F+Hh+W, D/2] per-axis tables (row = axis base + coordinate), fp32 for
+ * PARO_ROPE_REAL_F32 (pairs (2i,2i+1): o0=x0*c-x1*s, o1=x1*c+x0*s, as diffusers'
+ * apply_rotary_emb at cogvideox.py:167-172), fp64 for PARO_ROPE_COMPLEX_F64 (wan.py:161-164).
+ * pairs_f/pairs_h: how many leading channel pairs follow the f / h coordinate (rest: w).
+ * Replaces csrc/rope/rope.cu:14-48 (rope_permutation) and permute_qk / permute_attn_out
+ * (cogvideox.py:22-110). */
+int paro_rope_permute(const void* in, void* out, int dtype, int B, int H, int N, int D,
+                      int64_t stride_b, int64_t stride_h, int64_t stride_n,
+                      int n_text, int F, int Hh, int W, const int32_t* order_ids, int inverse,
+                      int rope_mode, const void* cos_tab, const void* sin_tab,
+                      int pairs_f, int pairs_h, paro_stream_t stream);
+
+/* ---- quantisers ------------------------------------------------------------------------ */
+
+/* Mean over tokens, [B,H,N,D] -> mean_out [B,H,D] in the input dtype (the `km` the reference
+ * expects from its caller, quant.py:46-48) and/or mean_f32 [B,H,D]; either may be NULL.
+ * Deterministic: fp64 partial sums in a fixed order.  scratch: paro_channel_stats_scratch_bytes. */
+size_t paro_channel_stats_scratch_bytes(int B, int H, int N, int D);
+int paro_channel_mean(const void* x, int dtype, int B, int H, int N, int D,
+                      int64_t stride_b, int64_t stride_h, int64_t stride_n,
+                      void* mean_out, float* mean_f32, void* scratch, size_t scratch_bytes,
+                      paro_stream_t stream);
+
+/* Per-group symmetric INT8: group = 32 (the reference's per-warp Q, quant.py:105-180 ->
+ * fused.cu:685-768) or 64 (per-block Q/K, fused.cu:429-682).  km (nullable, [B,H,D], input
+ * dtype) is subtracted first (fused.cu:594-682); fold_scale != 0 multiplies x before
+ * quantising (quant.py:91-96).  out: contiguous int8 [B,H,N,D]; scale: fp32
+ * [B,H,ceil(N/64)*(64/group)].  amax=max(1e-7,max|x|), scale=amax/127,
+ * q=sat(rint(x*(127/amax))) in IEEE fp32 (fused.cu:95-197, without its fast-math divide). */
+int paro_quant_int8(const void* x, int dtype, int B, int H, int N, int D,
+                    int64_t stride_b, int64_t stride_h, int64_t stride_n,
+                    const void* km, float fold_scale, int group,
+                    int8_t* out, float* scale, paro_stream_t stream);
+
+/* Per-channel FP8-e4m3 of V written token-contiguous: v8 [B,H,D,ceil64(N)] zero padded,
+ * v_scale [B,H,D] = amax/scale_max, vm [B,H,D] (mean, when smooth != 0).  v16 (nullable)
+ * receives the same e4m3 values widened to fp16, the operand format of paro_sparse_attn.
+ * Replaces per_channel_fp8 (quant.py:224-293 -> fused.cu:262-427); the 16-token shuffle of
+ * fused.cu:287-291 is an mma.sync artefact and is not applied. */
+int paro_quant_v_fp8(const void* v, int dtype, int B, int H, int N, int D,
+                     int64_t stride_b, int64_t stride_h, int64_t stride_n,
+                     int smooth, float scale_max, uint8_t* v8, uint16_t* v16,
+                     float* v_scale, float* vm, void* scratch, size_t scratch_bytes,
+                     paro_stream_t stream);
+
+/* ---- sparse plan ----------------------------------------------------------------------- */
+
+/* mask: bytes [slices, nbq, nbk], non-zero = keep (the `sparse` argument of
+ * csrc/qattn/qk_int_sv_f16_cuda_sm80.cu:53,222,268).  Step 1 writes the exclusive prefix
+ * sums row_ptr [slices*nbq+1] (kept blocks per q-block) and pair_ptr [slices*ceil(nbq/2)+1]
+ * (union of kept blocks per pair of adjacent q-blocks).  The caller reads the last element of
+ * each to size cols / pair_ent, then step 2 fills them: cols ascending kb per row; pair_ent
+ * ascending kb*4 + (keep(2p) | keep(2p+1)<<1). */
+int paro_plan_count(const uint8_t* mask, int slices, int nbq, int nbk,
+                    int32_t* row_ptr, int32_t* pair_ptr, paro_stream_t stream);
+int paro_plan_fill(const uint8_t* mask, int slices, int nbq, int nbk,
+                   const int32_t* row_ptr, int32_t* cols, int64_t cols_cap,
+                   const int32_t* pair_ptr, int32_t* pair_ent, int64_t pair_cap,
+                   paro_stream_t stream);
+
+/* ---- attention ------------------------------------------------------------------------- */
+
+/* Block-sparse attention over the kept 64x64 blocks with the inverse permutation fused
+ * into the output store.  Replaces qk_int8_sv_f16_accum_f16_attn
+ * (csrc/qattn/attn_cuda_sm80.h:19-30, qk_int_sv_f16_cuda_sm80.cu:905-1080) followed by
+ * permute_attn_out (cogvideox.py:64-110).
+ *   q8,k8: contiguous int8 [B,H,N,D]; q_scale [B,H,ceil(N/64)*(64/q_group)], k_scale
+ *   [B,H,ceil(N/64)]; v16: fp16 [B,H,D,ceil64(N)] (e4m3 values), v_scale/vm [B,H,D] (vm may
+ *   be NULL); pair_ptr/pair_ent from paro_plan_*, plan_slices = H (shared by the batch) or B*H;
+ *   inv_idx (nullable): table of paro_build_perm_index -- output row n_text+j of head h is
+ *   stored at token n_text+inv_idx[h][j]; out: [B,H,N,D] through element strides; lse
+ *   (nullable) fp32 [B,H,N] in output token order, natural log; status: int32[4] device
+ *   words, zero before the first call; a non-zero word 0 makes later launches return at once.
+ * S = (q8.k8^T) * q_scale * k_scale * sm_scale * log2(e); P = 2^(S - rowmax) over kept
+ * blocks and columns < N; O = (P.v16) / sum(P) * v_scale + vm. */
+int paro_sparse_attn(const int8_t* q8, const int8_t* k8, const uint16_t* v16,
+                     const float* q_scale, int q_group, const float* k_scale,
+                     const float* v_scale, const float* vm,
+                     const int32_t* pair_ptr, const int32_t* pair_ent, int plan_slices,
+                     const int32_t* inv_idx, int n_text,
+                     void* out, int out_dtype,
+                     int64_t out_stride_b, int64_t out_stride_h, int64_t out_stride_n,
+                     float* lse, int B, int H, int N, int D, float sm_scale,
+                     int32_t* status, paro_stream_t stream);
+
+/* Synchronises `stream`, copies the 4 status words to host_out (host pointer, may be NULL)
+ * and returns PARO_OK, PARO_ETIMEOUT (word 0 non-zero) or PARO_ECUDA. */
+int paro_status_poll(const int32_t* status, int32_t* host_out, paro_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PARO_B200_H */

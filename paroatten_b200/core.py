@@ -1,0 +1,199 @@
+"""Sparse-attention entry points (reference: paroattention/core.py)."""
+from __future__ import annotations
+
+from typing import Any, Optional, Sequence, Tuple, Union
+
+import torch
+import torch.nn.functional as F
+
+from . import _lib
+from .plan import CompactPlan, PermutePlan, SparsePlan, compact_plan, perm_index
+from .quant import _hnd, channel_mean, per_channel_fp8, per_warp_int8, per_block_int8
+from .rope import RopeTables, rope_permute
+
+_status = {}
+
+
+def _status_words(device: torch.device) -> torch.Tensor:
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    if key not in _status:
+        _status[key] = torch.zeros(4, dtype=torch.int32, device=device)
+    return _status[key]
+
+
+def check_status(device=None) -> None:
+    """Synchronises the current stream and raises if an attention launch on `device` gave up a
+    bounded wait (the launch's output is then invalid)."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    words = _status_words(device)
+    with torch.cuda.device(device):
+        rc = _lib.lib().paro_status_poll(words.data_ptr(), None, _lib.stream_ptr())
+        if rc != _lib.PARO_OK:
+            words.zero_()
+        _lib.check(rc)
+
+
+def sparse_attn_quantized(q_int8, q_scale, k_int8, k_scale, v_f16, v_scale, vm, plan: CompactPlan, sm_scale: float,
+                          out_dtype=torch.bfloat16, q_group: int = 32, inv_index: Optional[torch.Tensor] = None,
+                          n_text: int = 0, return_lse: bool = False, out: Optional[torch.Tensor] = None,
+                          out_layout: str = "HND"):
+    """The attention kernel on already quantised operands (HND, contiguous).
+    q_int8/k_int8 int8 [B,H,N,D]; q_scale [B,H,nb*(64/q_group)]; k_scale [B,H,nb];
+    v_f16 fp16 [B,H,D,ceil64(N)] holding e4m3 values; v_scale / vm fp32 [B,H,D] (vm may be None).
+    inv_index: int32 [H, N-n_text] table from plan.perm_index -- when given, the inverse token
+    permutation is applied as rows are stored.  Returns O [B,H,N,D] (or [B,N,H,D] when
+    out_layout="NHD") and, if asked, LSE [B,H,N] (natural log, in output token order)."""
+    _lib.require_cuda(q_int8, k_int8, v_f16, q_scale, k_scale, v_scale, vm, inv_index)
+    B, H, N, D = q_int8.shape
+    nb = (N + 63) // 64
+    if plan.nbq != nb or plan.nbk != nb:
+        raise ValueError(f"sparse plan is {plan.nbq}x{plan.nbk} blocks but the sequence has {nb}")
+    if plan.slices not in (H, B * H):
+        raise ValueError(f"sparse plan has {plan.slices} slices; expected H={H} or B*H={B * H}")
+    for t, name in ((q_int8, "q_int8"), (k_int8, "k_int8"), (v_f16, "v_f16")):
+        if not t.is_contiguous():
+            raise ValueError(f"{name} must be contiguous")
+    if tuple(v_f16.shape) != (B, H, D, nb * 64) or v_f16.dtype != torch.float16:
+        raise ValueError("v_f16 must be fp16 [B,H,D,ceil64(N)]")
+    dev = q_int8.device
+    with torch.cuda.device(dev):
+        if out is None:
+            shape = (B, H, N, D) if out_layout == "HND" else (B, N, H, D)
+            out = torch.empty(shape, dtype=out_dtype, device=dev)
+        ov = out if out_layout == "HND" else out.transpose(1, 2)
+        if tuple(ov.shape) != (B, H, N, D) or ov.stride(-1) != 1:
+            raise ValueError("out has the wrong shape or a strided last dimension")
+        lse = torch.empty(B, H, N, dtype=torch.float32, device=dev) if return_lse else None
+        _lib.check(_lib.lib().paro_sparse_attn(
+            q_int8.data_ptr(), k_int8.data_ptr(), v_f16.data_ptr(), q_scale.data_ptr(), int(q_group),
+            k_scale.data_ptr(), v_scale.data_ptr(), _lib.ptr(vm), plan.pair_ptr.data_ptr(), plan.pair_ent.data_ptr(),
+            plan.slices, _lib.ptr(inv_index), int(n_text), out.data_ptr(), _lib.dtype_code(out.dtype),
+            ov.stride(0), ov.stride(1), ov.stride(2), _lib.ptr(lse), B, H, N, D, float(sm_scale),
+            _status_words(dev).data_ptr(), _lib.stream_ptr()))
+    return (out, lse) if return_lse else out
+
+
+def _pad_head_dim(*ts):
+    """Pads head_dim up to 64 or 128 like the reference (core.py:181-192)."""
+    d = ts[0].size(-1)
+    if d > 128:
+        raise ValueError(f"Unsupported head_dim: {d}")
+    target = 64 if d <= 64 else 128
+    if d == target:
+        return ts, d
+    return tuple(F.pad(t, (0, target - d)) for t in ts), d
+
+
+def _as_plan(sparse: Union[torch.Tensor, CompactPlan]) -> CompactPlan:
+    return sparse if isinstance(sparse, CompactPlan) else compact_plan(sparse)
+
+
+@torch.compiler.disable
+def paroattn_qk_int8_pv_fp16_cuda(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+                                  sparse: Union[torch.Tensor, CompactPlan], tensor_layout: str = "HND",
+                                  is_causal: bool = False, qk_quant_gran: str = "per_warp",
+                                  sm_scale: Optional[float] = None, return_lse: bool = False,
+                                  smooth_k: bool = False, smooth_v: bool = True, **kwargs: Any):
+    """Same call as the reference operator (core.py:88-216): q, k, v are ALREADY in the
+    reordered token order, `sparse` is the boolean block mask `[B,H,nb,nb]` (or `[H,nb,nb]`,
+    shared by the batch; or an already compacted plan).  INT8 Q.K^T, fp16 P.V with fp32
+    accumulation.  Unlike the reference, V is first quantised per channel to FP8-e4m3 values
+    (carried as fp16), as the fake-quant emulation this library is checked against does.
+    smooth_k defaults to False as in the reference processors (cogvideox.py:186 passes no km).
+    `is_causal` is not supported (the video models never use it).  The returned LSE is that of
+    the scores the kernel saw (shifted by q.mean(k) per row when smooth_k is on)."""
+    dtype = q.dtype
+    assert q.is_cuda, "Input tensors must be on cuda."
+    assert dtype in [torch.float16, torch.bfloat16], "Input tensors must be in dtype of torch.float16 or torch.bfloat16"
+    assert qk_quant_gran in ["per_warp", "per_thread"], "qk_quant_gran must be either 'per_warp' or 'per_thread'."
+    assert q.device == k.device == v.device, "All tensors must be on the same device."
+    assert q.dtype == k.dtype == v.dtype, "All tensors must have the same dtype."
+    if is_causal:
+        raise ValueError("is_causal=True is not supported by paroatten_b200")
+    if tensor_layout not in ("HND", "NHD"):
+        raise ValueError(f"Unknown tensor layout: {tensor_layout}")
+    (q, k, v), head_dim_og = _pad_head_dim(q, k, v)
+    assert q.stride(-1) == 1 and k.stride(-1) == 1 and v.stride(-1) == 1, "Last dim of qkv must be contiguous."
+    if sm_scale is None:
+        sm_scale = head_dim_og ** -0.5
+    with torch.cuda.device(q.device):
+        km = channel_mean(k, tensor_layout) if smooth_k else None
+        if qk_quant_gran == "per_warp":
+            q8, qs, k8, ks = per_warp_int8(q, k, km, BLKQ=64, WARPQ=32, BLKK=64, tensor_layout=tensor_layout)
+            group, scale = 32, sm_scale
+        else:
+            # the reference's "per_thread" branch quantises per 64-token block with the softmax scale
+            # folded into Q (core.py:204-205, quant.py:91-96)
+            q8, qs, k8, ks = per_block_int8(q, k, km, BLKQ=64, BLKK=64, sm_scale=sm_scale, tensor_layout=tensor_layout)
+            group, scale = 64, 1.0 / 1.44269504
+        _, vs, vm, v16 = per_channel_fp8(v, tensor_layout, smooth_v=smooth_v, return_f16=True)
+        if tensor_layout == "NHD":
+            q8, k8 = q8.transpose(1, 2), k8.transpose(1, 2)  # back to the HND buffers
+        res = sparse_attn_quantized(q8, qs, k8, ks, v16, vs, vm, _as_plan(sparse), scale, out_dtype=dtype,
+                                    q_group=group, return_lse=return_lse, out_layout=tensor_layout)
+    o, lse = res if return_lse else (res, None)
+    o = o[..., :head_dim_og]
+    return (o, lse) if return_lse else o
+
+
+def paroattn(q, k, v, tensor_layout: str = "HND", is_causal: bool = False, sm_scale: Optional[float] = None,
+             return_lse: bool = False, sparse=None, **kwargs: Any):
+    """Reference dispatcher signature (core.py:13-85).  There is one implementation here
+    (sm_100a); `sparse` is required."""
+    if sparse is None:
+        raise ValueError("paroattn needs the block mask `sparse`")
+    major, minor = torch.cuda.get_device_capability(q.device)
+    if major != 10:
+        raise ValueError(f"Unsupported CUDA architecture: sm{major}{minor}")
+    return paroattn_qk_int8_pv_fp16_cuda(q, k, v, sparse, tensor_layout=tensor_layout, is_causal=is_causal,
+                                         sm_scale=sm_scale, return_lse=return_lse, **kwargs)
+
+
+def paro_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, permute_plan, sparse_plan, *,
+                   i_block: int = 0, i_timestep: int = 0, grid_fhw: Tuple[int, int, int], n_text: int = 0,
+                   rope: Optional[RopeTables] = None, tensor_layout: str = "HND", sm_scale: Optional[float] = None,
+                   smooth_k: bool = True, smooth_v: bool = True, return_lse: bool = False):
+    """The whole path of one self-attention layer, as the reference processors compose it
+    (cogvideox.py:167-227): q, k, v in NATURAL token order ->
+    RoPE on the video tokens of q, k + per-head F/H/W reordering of q, k, v (one fused pass each)
+    -> INT8 q (per 32 rows) / INT8 k (per 64 rows, mean-smoothed) / FP8 v
+    -> block-sparse attention over the kept blocks of sparse_plan[i_timestep, i_block]
+    -> output rows stored back in natural token order.
+
+    permute_plan: PermutePlan, or the reference's dict {'permute': [L,H]}, or int order ids [H].
+    sparse_plan: SparsePlan, the reference's [T,L,H,nb,nb] tensor, a mask [H,nb,nb] / [B,H,nb,nb],
+    or a CompactPlan."""
+    _lib.require_cuda(q, k, v)
+    if not (q.dtype == k.dtype == v.dtype) or q.dtype not in (torch.float16, torch.bfloat16):
+        raise ValueError("q, k, v must share dtype fp16 or bf16")
+    grid = tuple(int(g) for g in grid_fhw)
+    (q, k, v), head_dim_og = _pad_head_dim(q, k, v)
+    if sm_scale is None:
+        sm_scale = head_dim_og ** -0.5
+    dev = q.device
+    with torch.cuda.device(dev):
+        if isinstance(permute_plan, PermutePlan):
+            orders, index = permute_plan.orders(i_block), permute_plan.index(i_block)
+        else:
+            ids = permute_plan["permute"][i_block] if isinstance(permute_plan, dict) else permute_plan
+            orders = torch.as_tensor(ids).to(dev, torch.int32).contiguous()
+            index = perm_index(orders, grid, dev)
+        if isinstance(sparse_plan, SparsePlan):
+            plan = sparse_plan.get(i_timestep, i_block)
+        elif isinstance(sparse_plan, CompactPlan):
+            plan = sparse_plan
+        elif sparse_plan.dim() == 5:
+            plan = compact_plan(sparse_plan[i_timestep, i_block].to(dev))
+        else:
+            plan = compact_plan(sparse_plan.to(dev))
+        qp = rope_permute(q, orders, grid, n_text, rope, tensor_layout=tensor_layout)
+        kp = rope_permute(k, orders, grid, n_text, rope, tensor_layout=tensor_layout)
+        vp = rope_permute(v, orders, grid, n_text, None, tensor_layout=tensor_layout)
+        km = channel_mean(kp) if smooth_k else None
+        q8, qs, k8, ks = per_warp_int8(qp, kp, km, BLKQ=64, WARPQ=32, BLKK=64)
+        _, vs, vm, v16 = per_channel_fp8(vp, smooth_v=smooth_v, return_f16=True)
+        res = sparse_attn_quantized(q8, qs, k8, ks, v16, vs, vm, plan, sm_scale, out_dtype=q.dtype, q_group=32,
+                                    inv_index=index, n_text=n_text, return_lse=return_lse, out_layout=tensor_layout)
+    o, lse = res if return_lse else (res, None)
+    o = o[..., :head_dim_og]
+    return (o, lse) if return_lse else o

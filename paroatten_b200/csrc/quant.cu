@@ -1,0 +1,366 @@
+// INT8 quantisation of Q / mean-smoothed K and FP8-e4m3 quantisation of V.
+// All three are HBM-bound streaming kernels: 16-byte loads, every input element read once per
+// pass, results compared bit-for-bit with the CPU oracle (IEEE divide/multiply, no fast-math).
+#include <cuda_fp8.h>
+
+#include "common.cuh"
+
+namespace paro {
+
+constexpr int STATS_CHUNK = 512;  // tokens reduced by one CTA of the channel-statistics pass
+
+struct ChannelPartial {
+  double sum;
+  float mx, mn;
+};
+
+// ---------------------------------------------------------------------------------------------
+// Pass 1 of the per-channel reductions: per (b,h, chunk of tokens) the fp64 sum, max and min of
+// every channel.  Thread = one 8-channel slice of a token row; rows of the chunk are walked in a
+// fixed order and the cross-thread reduction is sequential, so results do not depend on timing.
+template <typename T, int D>
+__global__ void __launch_bounds__(256)
+channel_stats_kernel(const T* __restrict__ x, int H, int N, int64_t sb, int64_t sh, int64_t sn,
+                     ChannelPartial* __restrict__ part, int chunks) {
+  constexpr int TPR = D / 8;
+  constexpr int ROWS = 256 / TPR;
+  __shared__ double s_sum[ROWS][D + 1];
+  __shared__ float s_mx[ROWS][D + 1];
+  __shared__ float s_mn[ROWS][D + 1];
+  const int bh = blockIdx.y, b = bh / H, h = bh % H;
+  const int c8 = (threadIdx.x % TPR) * 8, r = threadIdx.x / TPR;
+  const int t0 = blockIdx.x * STATS_CHUNK, t1 = min(N, t0 + STATS_CHUNK);
+  const T* base = x + b * sb + h * sh;
+  double sum[8];
+  float mx[8], mn[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) { sum[j] = 0.0; mx[j] = -INFINITY; mn[j] = INFINITY; }
+  for (int t = t0 + r; t < t1; t += ROWS) {
+    Pack8<T> v;
+    v.v = *reinterpret_cast<const uint4*>(base + (size_t)t * sn + c8);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float f = F16Traits<T>::to_float(v.e[j]);
+      sum[j] += (double)f;
+      mx[j] = fmaxf(mx[j], f);
+      mn[j] = fminf(mn[j], f);
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) { s_sum[r][c8 + j] = sum[j]; s_mx[r][c8 + j] = mx[j]; s_mn[r][c8 + j] = mn[j]; }
+  __syncthreads();
+  if (threadIdx.x < D) {
+    double s = 0.0;
+    float a = -INFINITY, i = INFINITY;
+    for (int k = 0; k < ROWS; ++k) {
+      s += s_sum[k][threadIdx.x];
+      a = fmaxf(a, s_mx[k][threadIdx.x]);
+      i = fminf(i, s_mn[k][threadIdx.x]);
+    }
+    ChannelPartial p{s, a, i};
+    part[((size_t)bh * chunks + blockIdx.x) * D + threadIdx.x] = p;
+  }
+}
+
+// Pass 2: fold the chunk partials of one (b,h) in chunk order.
+// mean = fp32(sum/N); amax = max(1e-7, max(|max-mean|, |min-mean|)) (equal to max|x-mean|, the
+// form of fused.cu:385-389); scale = amax/scale_max.
+template <typename T>
+__global__ void channel_finalize_kernel(const ChannelPartial* __restrict__ part, int chunks, int D, int N,
+                                        int smooth, float scale_max, T* __restrict__ mean_t,
+                                        float* __restrict__ mean_f32, float* __restrict__ scale,
+                                        float* __restrict__ inv_out, float* __restrict__ mean_used) {
+  const int bh = blockIdx.x, d = threadIdx.x;
+  double s = 0.0;
+  float a = -INFINITY, i = INFINITY;
+  for (int c = 0; c < chunks; ++c) {
+    const ChannelPartial p = part[((size_t)bh * chunks + c) * D + d];
+    s += p.sum;
+    a = fmaxf(a, p.mx);
+    i = fminf(i, p.mn);
+  }
+  const float mean = smooth ? __double2float_rn(s / (double)N) : 0.0f;
+  if (mean_t) mean_t[(size_t)bh * D + d] = F16Traits<T>::from_float(__double2float_rn(s / (double)N));
+  if (mean_f32) mean_f32[(size_t)bh * D + d] = __double2float_rn(s / (double)N);
+  if (scale) {
+    const float amax = fmaxf(1e-7f, fmaxf(fabsf(__fsub_rn(a, mean)), fabsf(__fsub_rn(i, mean))));
+    scale[(size_t)bh * D + d] = __fdiv_rn(amax, scale_max);
+    inv_out[(size_t)bh * D + d] = __fdiv_rn(scale_max, amax);
+    mean_used[(size_t)bh * D + d] = mean;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// INT8: CTA = 128 threads = one 64-token block; warp w owns tokens 16w..16w+15.
+template <typename T, int D, int GROUP>
+__global__ void __launch_bounds__(128)
+quant_int8_kernel(const T* __restrict__ x, const T* __restrict__ km, int8_t* __restrict__ out,
+                  float* __restrict__ scale, int H, int N, int64_t sb, int64_t sh, int64_t sn,
+                  float fold, int n_scale_per_bh) {
+  constexpr int TPR = D / 8;          // threads per token row
+  constexpr int RPL = 32 / TPR;       // rows covered by one warp-wide load
+  constexpr int LOADS = 16 / RPL;     // loads per thread
+  __shared__ float s_amax[4];
+  const int bh = blockIdx.y, b = bh / H, h = bh % H;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int c8 = (lane % TPR) * 8;
+  const int tok0 = blockIdx.x * 64 + warp * 16 + lane / TPR;
+  const T* base = x + b * sb + h * sh;
+
+  float mean[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) mean[j] = 0.f;
+  if (km) {
+    Pack8<T> m;
+    m.v = *reinterpret_cast<const uint4*>(km + (size_t)bh * D + c8);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) mean[j] = F16Traits<T>::to_float(m.e[j]);
+  }
+
+  float v[LOADS][8];
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < LOADS; ++i) {
+    const int tok = tok0 + i * RPL;
+    if (tok < N) {
+      Pack8<T> p;
+      p.v = *reinterpret_cast<const uint4*>(base + (size_t)tok * sn + c8);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float f = F16Traits<T>::to_float(p.e[j]);
+        if (km) f = __fsub_rn(f, mean[j]);
+        if (fold != 0.f) f = __fmul_rn(f, fold);
+        v[i][j] = f;
+        amax = fmaxf(amax, fabsf(f));
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[i][j] = 0.f;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  if (lane == 0) s_amax[warp] = amax;
+  __syncthreads();
+  if (GROUP == 64) {
+    amax = fmaxf(fmaxf(s_amax[0], s_amax[1]), fmaxf(s_amax[2], s_amax[3]));
+  } else {
+    amax = fmaxf(s_amax[warp & ~1], s_amax[warp | 1]);
+  }
+  amax = fmaxf(amax, 1e-7f);
+  if (GROUP == 64) {
+    if (threadIdx.x == 0) scale[(size_t)bh * n_scale_per_bh + blockIdx.x] = __fdiv_rn(amax, 127.0f);
+  } else {
+    if (lane == 0 && (warp & 1) == 0)
+      scale[(size_t)bh * n_scale_per_bh + blockIdx.x * 2 + (warp >> 1)] = __fdiv_rn(amax, 127.0f);
+  }
+  const float inv = __fdiv_rn(127.0f, amax);
+#pragma unroll
+  for (int i = 0; i < LOADS; ++i) {
+    const int tok = tok0 + i * RPL;
+    if (tok < N) {
+      uint32_t w[2];
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t acc = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          int q = __float2int_rn(__fmul_rn(v[i][half * 4 + j], inv));
+          q = max(-128, min(127, q));
+          acc |= (uint32_t)(q & 0xff) << (8 * j);
+        }
+        w[half] = acc;
+      }
+      *reinterpret_cast<uint2*>(out + ((size_t)bh * N + tok) * D + c8) = make_uint2(w[0], w[1]);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// FP8 cast + transpose: CTA = 256 threads = one 64-token block of one (b,h).
+// Phase 1 stages the raw tile in shared memory with coalesced 16-byte loads; phase 2 lets
+// consecutive lanes take consecutive channels (conflict-free column reads) and each thread emit a
+// run of tokens of its channel as whole 32-byte sectors.
+template <typename T, int D>
+__global__ void __launch_bounds__(256)
+quant_v_fp8_kernel(const T* __restrict__ v, int H, int N, int npad, int64_t sb, int64_t sh, int64_t sn,
+                   const float* __restrict__ inv_tab, const float* __restrict__ mean_tab,
+                   uint8_t* __restrict__ v8, __half* __restrict__ v16) {
+  constexpr int TPR = D / 8;
+  constexpr int ROWS = 256 / TPR;
+  constexpr int LD = D + 8;                 // padded row, keeps 16-byte alignment
+  constexpr int RUN = 64 / (256 / D);       // tokens per thread in phase 2 (32 for D=128, 16 for D=64)
+  __shared__ __align__(16) T tile[64 * LD];
+  const int bh = blockIdx.y, b = bh / H, h = bh % H;
+  const int t0 = blockIdx.x * 64;
+  const T* base = v + b * sb + h * sh;
+  {
+    const int c8 = (threadIdx.x % TPR) * 8;
+#pragma unroll
+    for (int r = threadIdx.x / TPR; r < 64; r += ROWS) {
+      uint4 val = make_uint4(0, 0, 0, 0);
+      if (t0 + r < N) val = *reinterpret_cast<const uint4*>(base + (size_t)(t0 + r) * sn + c8);
+      *reinterpret_cast<uint4*>(&tile[r * LD + c8]) = val;
+    }
+  }
+  __syncthreads();
+  const int d = threadIdx.x % D, run = threadIdx.x / D;
+  const float mean = mean_tab[(size_t)bh * D + d];
+  const float inv = inv_tab[(size_t)bh * D + d];  // scale_max / amax, from the finalize pass
+  uint32_t w8[RUN / 4];
+  uint32_t w16[RUN / 2];
+#pragma unroll
+  for (int i = 0; i < RUN; i += 2) {
+    float y[2];
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int r = run * RUN + i + k;
+      float f = 0.f;
+      if (t0 + r < N) f = __fmul_rn(__fsub_rn(F16Traits<T>::to_float(tile[r * LD + d]), mean), inv);
+      y[k] = f;
+    }
+    const __nv_fp8x2_storage_t p = __nv_cvt_float2_to_fp8x2(make_float2(y[0], y[1]), __NV_SATFINITE, __NV_E4M3);
+    if ((i & 3) == 0) w8[i / 4] = (uint32_t)p; else w8[i / 4] |= (uint32_t)p << 16;
+    const __half2_raw h2 = __nv_cvt_fp8x2_to_halfraw2(p, __NV_E4M3);
+    w16[i / 2] = (uint32_t)h2.x | ((uint32_t)h2.y << 16);
+  }
+  const size_t o = ((size_t)bh * D + d) * npad + t0 + run * RUN;
+#pragma unroll
+  for (int i = 0; i < RUN / 16; ++i)
+    *reinterpret_cast<uint4*>(v8 + o + i * 16) = make_uint4(w8[4 * i], w8[4 * i + 1], w8[4 * i + 2], w8[4 * i + 3]);
+  if (v16) {
+#pragma unroll
+    for (int i = 0; i < RUN / 8; ++i)
+      *reinterpret_cast<uint4*>(v16 + o + i * 8) = make_uint4(w16[4 * i], w16[4 * i + 1], w16[4 * i + 2], w16[4 * i + 3]);
+  }
+}
+
+}  // namespace paro
+
+using namespace paro;
+
+namespace {
+
+int stats_chunks(int N) { return (N + STATS_CHUNK - 1) / STATS_CHUNK; }
+
+// scratch = partials [B*H*chunks*D] followed by two fp32 tables [B*H*D] (scale_max/amax, mean used)
+size_t stats_bytes(int B, int H, int N, int D) {
+  const size_t bh = (size_t)B * H;
+  return bh * stats_chunks(N) * D * sizeof(ChannelPartial) + 2 * bh * D * sizeof(float);
+}
+
+template <typename T>
+void launch_stats(const void* x, int B, int H, int N, int D, int64_t sb, int64_t sh, int64_t sn,
+                  ChannelPartial* part, cudaStream_t s) {
+  dim3 grid(stats_chunks(N), B * H);
+  if (D == 128)
+    channel_stats_kernel<T, 128><<<grid, 256, 0, s>>>((const T*)x, H, N, sb, sh, sn, part, stats_chunks(N));
+  else
+    channel_stats_kernel<T, 64><<<grid, 256, 0, s>>>((const T*)x, H, N, sb, sh, sn, part, stats_chunks(N));
+}
+
+}  // namespace
+
+extern "C" size_t paro_channel_stats_scratch_bytes(int B, int H, int N, int D) {
+  if (B <= 0 || H <= 0 || N <= 0 || (D != 64 && D != 128)) return 0;
+  return stats_bytes(B, H, N, D);
+}
+
+extern "C" int paro_channel_mean(const void* x, int dtype, int B, int H, int N, int D,
+                                 int64_t stride_b, int64_t stride_h, int64_t stride_n,
+                                 void* mean_out, float* mean_f32, void* scratch, size_t scratch_bytes,
+                                 paro_stream_t stream) {
+  if (int rc = check_tensor("paro_channel_mean(x)", x, dtype, B, H, N, D, stride_b, stride_h, stride_n)) return rc;
+  PARO_REQUIRE(mean_out || mean_f32, PARO_EINVAL, "paro_channel_mean: no output requested");
+  PARO_REQUIRE(scratch && scratch_bytes >= stats_bytes(B, H, N, D), PARO_ECAP,
+               "paro_channel_mean: scratch too small (%zu < %zu)", scratch_bytes, stats_bytes(B, H, N, D));
+  PARO_REQUIRE(aligned16(scratch), PARO_EALIGN, "paro_channel_mean: scratch not 16-byte aligned");
+  cudaStream_t s = (cudaStream_t)stream;
+  ChannelPartial* part = static_cast<ChannelPartial*>(scratch);
+  if (dtype == PARO_F16) {
+    launch_stats<__half>(x, B, H, N, D, stride_b, stride_h, stride_n, part, s);
+    channel_finalize_kernel<__half><<<B * H, D, 0, s>>>(part, stats_chunks(N), D, N, 1, 1.f, (__half*)mean_out,
+                                                        mean_f32, nullptr, nullptr, nullptr);
+  } else {
+    launch_stats<__nv_bfloat16>(x, B, H, N, D, stride_b, stride_h, stride_n, part, s);
+    channel_finalize_kernel<__nv_bfloat16><<<B * H, D, 0, s>>>(part, stats_chunks(N), D, N, 1, 1.f,
+                                                               (__nv_bfloat16*)mean_out, mean_f32, nullptr, nullptr,
+                                                               nullptr);
+  }
+  return check_launch("channel_mean");
+}
+
+namespace {
+template <typename T, int D>
+int launch_int8(const void* x, const void* km, int8_t* out, float* scale, int B, int H, int N, int64_t sb,
+                int64_t sh, int64_t sn, float fold, int group, cudaStream_t s) {
+  const int nb = (N + 63) / 64;
+  dim3 grid(nb, B * H);
+  if (group == 64)
+    quant_int8_kernel<T, D, 64><<<grid, 128, 0, s>>>((const T*)x, (const T*)km, out, scale, H, N, sb, sh, sn, fold, nb);
+  else
+    quant_int8_kernel<T, D, 32><<<grid, 128, 0, s>>>((const T*)x, (const T*)km, out, scale, H, N, sb, sh, sn, fold,
+                                                     nb * 2);
+  return check_launch("quant_int8_kernel");
+}
+}  // namespace
+
+extern "C" int paro_quant_int8(const void* x, int dtype, int B, int H, int N, int D,
+                               int64_t stride_b, int64_t stride_h, int64_t stride_n,
+                               const void* km, float fold_scale, int group,
+                               int8_t* out, float* scale, paro_stream_t stream) {
+  if (int rc = check_tensor("paro_quant_int8(x)", x, dtype, B, H, N, D, stride_b, stride_h, stride_n)) return rc;
+  PARO_REQUIRE(group == 32 || group == 64, PARO_EINVAL, "paro_quant_int8: group must be 32 or 64, got %d", group);
+  PARO_REQUIRE(out && scale, PARO_EINVAL, "paro_quant_int8: null output");
+  PARO_REQUIRE(aligned16(out) && (!km || aligned16(km)), PARO_EALIGN, "paro_quant_int8: out/km not 16-byte aligned");
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == PARO_F16)
+    return D == 128 ? launch_int8<__half, 128>(x, km, out, scale, B, H, N, stride_b, stride_h, stride_n, fold_scale, group, s)
+                    : launch_int8<__half, 64>(x, km, out, scale, B, H, N, stride_b, stride_h, stride_n, fold_scale, group, s);
+  return D == 128 ? launch_int8<__nv_bfloat16, 128>(x, km, out, scale, B, H, N, stride_b, stride_h, stride_n, fold_scale, group, s)
+                  : launch_int8<__nv_bfloat16, 64>(x, km, out, scale, B, H, N, stride_b, stride_h, stride_n, fold_scale, group, s);
+}
+
+namespace {
+template <typename T>
+int run_v_fp8(const void* v, int B, int H, int N, int D, int64_t sb, int64_t sh, int64_t sn, int smooth,
+              float scale_max, uint8_t* v8, uint16_t* v16, float* v_scale, float* vm, void* scratch,
+              cudaStream_t s) {
+  const int chunks = stats_chunks(N);
+  const size_t bh = (size_t)B * H;
+  ChannelPartial* part = static_cast<ChannelPartial*>(scratch);
+  float* inv_tab = reinterpret_cast<float*>(part + bh * chunks * D);
+  float* mean_tab = inv_tab + bh * D;
+  launch_stats<T>(v, B, H, N, D, sb, sh, sn, part, s);
+  channel_finalize_kernel<T><<<B * H, D, 0, s>>>(part, chunks, D, N, smooth, scale_max, (T*)nullptr,
+                                                 smooth ? vm : nullptr, v_scale, inv_tab, mean_tab);
+  const int npad = (N + 63) / 64 * 64;
+  dim3 grid(npad / 64, B * H);
+  if (D == 128)
+    quant_v_fp8_kernel<T, 128><<<grid, 256, 0, s>>>((const T*)v, H, N, npad, sb, sh, sn, inv_tab, mean_tab, v8,
+                                                    (__half*)v16);
+  else
+    quant_v_fp8_kernel<T, 64><<<grid, 256, 0, s>>>((const T*)v, H, N, npad, sb, sh, sn, inv_tab, mean_tab, v8,
+                                                   (__half*)v16);
+  return check_launch("quant_v_fp8");
+}
+}  // namespace
+
+extern "C" int paro_quant_v_fp8(const void* v, int dtype, int B, int H, int N, int D,
+                                int64_t stride_b, int64_t stride_h, int64_t stride_n,
+                                int smooth, float scale_max, uint8_t* v8, uint16_t* v16,
+                                float* v_scale, float* vm, void* scratch, size_t scratch_bytes,
+                                paro_stream_t stream) {
+  if (int rc = check_tensor("paro_quant_v_fp8(v)", v, dtype, B, H, N, D, stride_b, stride_h, stride_n)) return rc;
+  PARO_REQUIRE(v8 && v_scale, PARO_EINVAL, "paro_quant_v_fp8: null output");
+  PARO_REQUIRE(!smooth || vm, PARO_EINVAL, "paro_quant_v_fp8: smoothing needs the vm output");
+  PARO_REQUIRE(scale_max > 0.f && scale_max <= 448.f, PARO_EINVAL, "paro_quant_v_fp8: scale_max must be in (0, 448]");
+  PARO_REQUIRE(aligned16(v8) && (!v16 || aligned16(v16)), PARO_EALIGN, "paro_quant_v_fp8: outputs not 16-byte aligned");
+  PARO_REQUIRE(scratch && scratch_bytes >= stats_bytes(B, H, N, D), PARO_ECAP,
+               "paro_quant_v_fp8: scratch too small (%zu < %zu)", scratch_bytes, stats_bytes(B, H, N, D));
+  PARO_REQUIRE(aligned16(scratch), PARO_EALIGN, "paro_quant_v_fp8: scratch not 16-byte aligned");
+  cudaStream_t s = (cudaStream_t)stream;
+  return dtype == PARO_F16
+             ? run_v_fp8<__half>(v, B, H, N, D, stride_b, stride_h, stride_n, smooth, scale_max, v8, v16, v_scale, vm, scratch, s)
+             : run_v_fp8<__nv_bfloat16>(v, B, H, N, D, stride_b, stride_h, stride_n, smooth, scale_max, v8, v16, v_scale, vm, scratch, s);
+}

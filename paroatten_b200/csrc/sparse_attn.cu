@@ -1,0 +1,448 @@
+// Block-sparse attention over kept 64x64 blocks for sm_100a.
+//
+// Work item (one CTA): a PAIR of adjacent 64-row q-blocks of one (batch, head), i.e. a 128-row
+// tile -- the native tcgen05.mma M -- walking the union of the two blocks' kept k-blocks.  Each list
+// entry says which of the two halves keeps the block; the half that does not is given P = 0.
+//
+//   warp 0     TMA producer: Q tile once, then K (int8) and V^T (fp16) tiles through a ring
+//   warp 1     owns TMEM; one lane issues S = Q.K^T (kind::i8, int32 accumulators in TMEM) and
+//              O += P.V (kind::f16, P read from TMEM, fp32 accumulators in TMEM)
+//   warps 2-5  one thread per q row: online softmax in fp32 (base 2, lazy rescaling), P written
+//              back over S in TMEM as fp16, epilogue O/l * v_scale + vm stored to the row's
+//              un-permuted position.
+//
+// S is double buffered so that QK^T of tile i+1 overlaps the softmax of tile i; two CTAs share an
+// SM so that one CTA's softmax overlaps the other's MMAs.  Every wait is bounded: on expiry the
+// CTA records a code in the status words, raises a shared abort flag and unwinds (TMEM freed).
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <mutex>
+
+#include "common.cuh"
+#include "umma.cuh"
+
+namespace paro {
+
+using namespace umma;
+
+constexpr int ATT_THREADS = 192;
+constexpr int TMEM_COLS = 256;              // S0 [0,64) S1 [64,128) O [128,128+D)
+constexpr long long WAIT_LIMIT = 400000000; // SM cycles (~0.2 s) before a wait gives up
+constexpr float RESCALE_TAU = 8.0f;         // rescale O only when the row max grows by > 2^8
+
+template <int D> struct AttnCfg {
+  static constexpr int STAGES = (D == 128) ? 3 : 6;   // sized so that exactly two CTAs fit an SM
+  static constexpr int Q_BYTES = 128 * D;
+  static constexpr int K_BYTES = 64 * D;
+  static constexpr int V_BYTES = D * 128;   // D rows of 64 fp16
+  static constexpr int TILE_BYTES = Q_BYTES + STAGES * (K_BYTES + V_BYTES);
+  static constexpr int AUX_BYTES = 2048;    // barriers, TMEM pointer, abort flag, v_scale, vm
+  static constexpr int SMEM_BYTES = TILE_BYTES + AUX_BYTES + 1024 /* alignment slack */;
+};
+
+struct AttnParams {
+  const float* q_scale;
+  const float* k_scale;
+  const float* v_scale;
+  const float* vm;
+  const int32_t* pair_ptr;
+  const int32_t* pair_ent;
+  const int32_t* inv_idx;
+  void* out;
+  float* lse;
+  int32_t* status;
+  int64_t osb, osh, osn;
+  int plan_slices, q_group, n_text;
+  int B, H, N, npairs, nb;
+  float scale_log2;  // sm_scale * log2(e)
+};
+
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__device__ __forceinline__ void report_timeout(const AttnParams& p, volatile int* abort_flag, int where, int iter) {
+  if (atomicCAS(p.status, 0, PARO_ETIMEOUT) == 0) {
+    p.status[1] = where;
+    p.status[2] = (int)blockIdx.x;
+    p.status[3] = iter;
+  }
+  *abort_flag = 1;
+}
+
+#define ATT_WAIT(bar, parity, where, iter)                                   \
+  if (!mbar_wait_bounded((bar), (parity), abort_flag, WAIT_LIMIT)) {         \
+    report_timeout(p, abort_flag, (where), (iter));                          \
+    break;                                                                   \
+  }
+
+template <int D, typename OutT>
+__global__ void __launch_bounds__(ATT_THREADS, 2)
+sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                   const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
+  using Cfg = AttnCfg<D>;
+  constexpr int NST = Cfg::STAGES;
+  if (*reinterpret_cast<volatile int32_t*>(p.status) != 0) return;  // an earlier CTA failed: drain quickly
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sK = sQ + Cfg::Q_BYTES;
+  uint8_t* sV = sK + NST * Cfg::K_BYTES;
+  uint8_t* aux = smem + Cfg::TILE_BYTES;
+  uint64_t* bar_q = reinterpret_cast<uint64_t*>(aux);   // [1]
+  uint64_t* bar_kfull = bar_q + 1;                      // [NST]
+  uint64_t* bar_vfull = bar_kfull + NST;                // [NST]
+  uint64_t* bar_empty = bar_vfull + NST;                // [NST]
+  uint64_t* bar_sfull = bar_empty + NST;                // [2]
+  uint64_t* bar_pready = bar_sfull + 2;                 // [2]
+  uint64_t* bar_pvdone = bar_pready + 2;                // [1]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_pvdone + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* s_vscale = reinterpret_cast<float*>(aux + 256);
+  float* s_vm = s_vscale + D;
+  static_assert(256 + 2 * D * 4 <= Cfg::AUX_BYTES, "aux area too small");
+  static_assert((6 + 3 * NST) * 8 + 8 <= 256, "barrier area too small");
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int bh = blockIdx.x / p.npairs, pair = blockIdx.x % p.npairs;
+  const int slice = bh % p.plan_slices;
+  const int ent0 = p.pair_ptr[slice * p.npairs + pair];
+  const int n_ent = p.pair_ptr[slice * p.npairs + pair + 1] - ent0;
+  const int32_t* ent = p.pair_ent + ent0;
+
+  if (threadIdx.x == 0) {
+    mbar_init(bar_q, 1);
+    for (int i = 0; i < NST; ++i) {
+      mbar_init(bar_kfull + i, 1);
+      mbar_init(bar_vfull + i, 1);
+      mbar_init(bar_empty + i, 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar_sfull + i, 1);
+      mbar_init(bar_pready + i, 128);
+    }
+    mbar_init(bar_pvdone, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tS[2] = {tmem_base, tmem_base + 64u};
+  const uint32_t tO = tmem_base + 128u;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tm_q);
+      tma_prefetch_desc(&tm_k);
+      tma_prefetch_desc(&tm_v);
+      mbar_arrive_expect_tx(bar_q, Cfg::Q_BYTES);
+      tma_load_3d(sQ, &tm_q, 0, pair * 128, bh, bar_q);
+      for (int i = 0; i < n_ent; ++i) {
+        const int st = i % NST, use = i / NST;
+        if (use > 0) { ATT_WAIT(bar_empty + st, (use - 1) & 1, 1, i) }
+        const int kb = ent[i] >> 2;
+        mbar_arrive_expect_tx(bar_kfull + st, Cfg::K_BYTES);
+        tma_load_3d(sK + st * Cfg::K_BYTES, &tm_k, 0, kb * 64, bh, bar_kfull + st);
+        mbar_arrive_expect_tx(bar_vfull + st, Cfg::V_BYTES);
+        tma_load_3d(sV + st * Cfg::V_BYTES, &tm_v, kb * 64, 0, bh, bar_vfull + st);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t IDESC_QK = instr_desc(2, 1, 1, 128, 64);  // s32 += s8 * s8
+      constexpr uint32_t IDESC_PV = instr_desc(1, 0, 0, 128, D);   // f32 += f16 * f16
+      const uint64_t dQ = smem_desc(smem_u32(sQ), D);
+      auto issue_qk = [&](int i) {
+        const uint64_t dK = smem_desc(smem_u32(sK + (i % NST) * Cfg::K_BYTES), D);
+#pragma unroll
+        for (int k = 0; k < D / 32; ++k)
+          mma_i8_ss(tS[i & 1], desc_advance(dQ, 32 * k), desc_advance(dK, 32 * k), IDESC_QK, k > 0);
+        mma_commit(bar_sfull + (i & 1));
+      };
+      do {
+        ATT_WAIT(bar_q, 0, 2, -1)
+        if (n_ent == 0) break;
+        ATT_WAIT(bar_kfull + 0, 0, 3, 0)
+        tc_fence_after();
+        issue_qk(0);
+        for (int i = 0; i < n_ent; ++i) {
+          const int st = i % NST;
+          if (i + 1 < n_ent) {
+            ATT_WAIT(bar_kfull + (i + 1) % NST, ((i + 1) / NST) & 1, 3, i + 1)
+            tc_fence_after();
+            issue_qk(i + 1);
+          }
+          ATT_WAIT(bar_pready + (i & 1), (i >> 1) & 1, 4, i)
+          ATT_WAIT(bar_vfull + st, (i / NST) & 1, 5, i)
+          tc_fence_after();
+          const uint64_t dV = smem_desc(smem_u32(sV + st * Cfg::V_BYTES), 128);
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            mma_f16_ts(tO, tS[i & 1] + 8 * k, desc_advance(dV, 32 * k), IDESC_PV, (i > 0 || k > 0) ? 1u : 0u);
+          mma_commit(bar_empty + st);
+          mma_commit(bar_pvdone);
+        }
+      } while (false);
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax + epilogue
+    const int qd = warp & 3;                 // TMEM lane quadrant this warp may touch
+    const int r = qd * 32 + lane;            // row inside the 128-row tile
+    const int half = qd >> 1;                // which q-block of the pair
+    const uint32_t lane_off = (uint32_t)(qd * 32) << 16;
+    const int tid = threadIdx.x - 64;
+    if (tid < D) {
+      s_vscale[tid] = p.v_scale[(size_t)bh * D + tid];
+      s_vm[tid] = p.vm ? p.vm[(size_t)bh * D + tid] : 0.f;
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+
+    const int tok = pair * 128 + r;
+    const int per_bh = p.nb * (64 / p.q_group);
+    const float rowscale = (tok < p.N ? p.q_scale[(size_t)bh * per_bh + tok / p.q_group] : 0.f) * p.scale_log2;
+    float m = -INFINITY, l = 0.f;
+    bool ok = true;
+
+    for (int i = 0; i < n_ent; ++i) {
+      const int e = ent[i];
+      const int kb = e >> 2;
+      const bool keep = (e >> half) & 1;
+      ok = __all_sync(0xffffffffu, mbar_wait_bounded(bar_sfull + (i & 1), (i >> 1) & 1, abort_flag, WAIT_LIMIT));
+      if (!ok) {
+        report_timeout(p, abort_flag, 6, i);
+        break;
+      }
+      tc_fence_after();
+      uint32_t pk[32];
+      if (keep) {
+        uint32_t s[64];
+        tmem_ld32(tS[i & 1] + lane_off, s);
+        tmem_ld32(tS[i & 1] + lane_off + 32, s + 32);
+        tmem_wait_ld();
+        const int valid = min(64, p.N - kb * 64);
+        const float sc = rowscale * p.k_scale[(size_t)bh * p.nb + kb];
+        int imax = INT_MIN;
+#pragma unroll
+        for (int j = 0; j < 64; ++j)
+          if (j < valid) imax = max(imax, (int)s[j]);
+        const float mx = (float)imax * sc;
+        float alpha = 1.f;
+        bool resc = false;
+        if (mx > m + RESCALE_TAU) {
+          alpha = ex2_approx(m - mx);     // 0 when m = -inf
+          resc = m > -INFINITY;
+          m = mx;
+          l *= alpha;
+        }
+        if (__any_sync(0xffffffffu, resc)) {
+          // O may only be touched once the previous P.V has landed
+          ok = __all_sync(0xffffffffu, mbar_wait_bounded(bar_pvdone, (i - 1) & 1, abort_flag, WAIT_LIMIT));
+          if (!ok) {
+            report_timeout(p, abort_flag, 7, i);
+            break;
+          }
+          tc_fence_after();
+#pragma unroll
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t o[32];
+            tmem_ld32(tO + lane_off + 32 * c, o);
+            tmem_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
+            tmem_st32(tO + lane_off + 32 * c, o);
+          }
+          tmem_wait_st();
+        }
+        const float negm = -m;
+        float sum = 0.f;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          float p0 = ex2_approx(fmaf((float)(int)s[2 * j], sc, negm));
+          float p1 = ex2_approx(fmaf((float)(int)s[2 * j + 1], sc, negm));
+          if (2 * j >= valid) p0 = 0.f;
+          if (2 * j + 1 >= valid) p1 = 0.f;
+          sum += p0 + p1;
+          const __half2 h2 = __floats2half2_rn(p0, p1);
+          pk[j] = *reinterpret_cast<const uint32_t*>(&h2);
+        }
+        l += sum;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) pk[j] = 0u;
+      }
+      tmem_st32(tS[i & 1] + lane_off, pk);
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(bar_pready + (i & 1));
+    }
+
+    // epilogue (the TMEM loads are warp-collective: every lane of the warp executes them, rows past
+    // the end of the sequence only skip the store)
+    if (ok && n_ent > 0) {
+      ok = __all_sync(0xffffffffu, mbar_wait_bounded(bar_pvdone, (n_ent - 1) & 1, abort_flag, WAIT_LIMIT));
+      if (!ok) report_timeout(p, abort_flag, 8, n_ent);
+      tc_fence_after();
+    }
+    if (ok) {
+      const int b = bh / p.H, h = bh % p.H;
+      const bool live = tok < p.N;
+      int dst = tok;
+      if (live && p.inv_idx && tok >= p.n_text)
+        dst = p.n_text + p.inv_idx[(size_t)h * (p.N - p.n_text) + (tok - p.n_text)];
+      OutT* orow = static_cast<OutT*>(p.out) + b * p.osb + h * p.osh + (int64_t)dst * p.osn;
+      const float inv_l = l > 0.f ? 1.f / l : 0.f;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t o[32];
+        if (n_ent > 0) {
+          tmem_ld32(tO + lane_off + 32 * c, o);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) o[j] = 0u;
+        }
+        uint32_t w[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int d0 = 32 * c + 2 * j;
+          const float a0 = l > 0.f ? fmaf(__uint_as_float(o[2 * j]) * inv_l, s_vscale[d0], s_vm[d0]) : 0.f;
+          const float a1 = l > 0.f ? fmaf(__uint_as_float(o[2 * j + 1]) * inv_l, s_vscale[d0 + 1], s_vm[d0 + 1]) : 0.f;
+          OutT t[2] = {F16Traits<OutT>::from_float(a0), F16Traits<OutT>::from_float(a1)};
+          w[j] = *reinterpret_cast<const uint32_t*>(t);
+        }
+        if (live) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            *reinterpret_cast<uint4*>(orow + 32 * c + 8 * j) = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+        }
+      }
+      if (live && p.lse) p.lse[(size_t)bh * p.N + dst] = l > 0.f ? (log2f(l) + m) * 0.6931471805599453f : -INFINITY;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  });
+  return fn;
+}
+
+// 3-D map over a tensor [d2][d1][d0] of `esize`-byte elements, box [1][box1][box0].
+static int make_map(CUtensorMap* map, CUtensorMapDataType dt, int esize, const void* base, uint64_t d0, uint64_t d1,
+                    uint64_t d2, uint32_t box0, uint32_t box1, CUtensorMapSwizzle swz) {
+  EncodeTiledFn fn = encode_fn();
+  PARO_REQUIRE(fn != nullptr, PARO_ECUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t dims[3] = {d0, d1, d2};
+  cuuint64_t strides[2] = {d0 * esize, d0 * d1 * esize};
+  cuuint32_t box[3] = {box0, box1, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult rc = fn(map, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  PARO_REQUIRE(rc == CUDA_SUCCESS, PARO_ECUDA, "cuTensorMapEncodeTiled failed with code %d", (int)rc);
+  return PARO_OK;
+}
+
+template <int D, typename OutT>
+static int launch_attn(const int8_t* q8, const int8_t* k8, const uint16_t* v16, const AttnParams& p, cudaStream_t s) {
+  using Cfg = AttnCfg<D>;
+  const uint64_t BH = (uint64_t)p.B * p.H;
+  const uint64_t npad = (uint64_t)p.nb * 64;
+  const CUtensorMapSwizzle swz_qk = D == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+  CUtensorMap tq, tk, tv;
+  if (int rc = make_map(&tq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, q8, D, p.N, BH, D, 128, swz_qk)) return rc;
+  if (int rc = make_map(&tk, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, k8, D, p.N, BH, D, 64, swz_qk)) return rc;
+  if (int rc = make_map(&tv, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, v16, npad, D, BH, 64, D, CU_TENSOR_MAP_SWIZZLE_128B))
+    return rc;
+  auto kern = sparse_attn_kernel<D, OutT>;
+  PARO_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+  const uint64_t ctas = BH * p.npairs;
+  PARO_REQUIRE(ctas < (1ull << 31), PARO_ESHAPE, "paro_sparse_attn: too many work items");
+  kern<<<(unsigned)ctas, ATT_THREADS, Cfg::SMEM_BYTES, s>>>(tq, tk, tv, p);
+  return check_launch("sparse_attn_kernel");
+}
+
+}  // namespace paro
+
+using namespace paro;
+
+extern "C" int paro_sparse_attn(const int8_t* q8, const int8_t* k8, const uint16_t* v16,
+                                const float* q_scale, int q_group, const float* k_scale,
+                                const float* v_scale, const float* vm,
+                                const int32_t* pair_ptr, const int32_t* pair_ent, int plan_slices,
+                                const int32_t* inv_idx, int n_text,
+                                void* out, int out_dtype,
+                                int64_t out_stride_b, int64_t out_stride_h, int64_t out_stride_n,
+                                float* lse, int B, int H, int N, int D, float sm_scale,
+                                int32_t* status, paro_stream_t stream) {
+  PARO_REQUIRE(q8 && k8 && v16 && q_scale && k_scale && v_scale && pair_ptr && pair_ent && out && status, PARO_EINVAL,
+               "paro_sparse_attn: null pointer");
+  PARO_REQUIRE(B > 0 && H > 0 && N > 0, PARO_ESHAPE, "paro_sparse_attn: empty problem");
+  PARO_REQUIRE(D == 64 || D == 128, PARO_ESHAPE, "paro_sparse_attn: head_dim %d unsupported (64 or 128)", D);
+  PARO_REQUIRE(q_group == 32 || q_group == 64, PARO_EINVAL, "paro_sparse_attn: q_group must be 32 or 64");
+  PARO_REQUIRE(out_dtype == PARO_F16 || out_dtype == PARO_BF16, PARO_EINVAL, "paro_sparse_attn: bad out_dtype");
+  PARO_REQUIRE(plan_slices == H || plan_slices == B * H, PARO_ESHAPE,
+               "paro_sparse_attn: plan_slices must be H or B*H (got %d)", plan_slices);
+  PARO_REQUIRE(n_text >= 0 && n_text <= N, PARO_ESHAPE, "paro_sparse_attn: n_text out of range");
+  PARO_REQUIRE(aligned16(q8) && aligned16(k8) && aligned16(v16) && aligned16(out), PARO_EALIGN,
+               "paro_sparse_attn: q8/k8/v16/out must be 16-byte aligned");
+  PARO_REQUIRE(out_stride_b % 8 == 0 && out_stride_h % 8 == 0 && out_stride_n % 8 == 0 && out_stride_n >= D,
+               PARO_EALIGN, "paro_sparse_attn: output strides must be multiples of 8 elements");
+  PARO_REQUIRE(sm_scale > 0.f, PARO_EINVAL, "paro_sparse_attn: sm_scale must be positive");
+  AttnParams p;
+  p.q_scale = q_scale; p.k_scale = k_scale; p.v_scale = v_scale; p.vm = vm;
+  p.pair_ptr = pair_ptr; p.pair_ent = pair_ent; p.inv_idx = inv_idx;
+  p.out = out; p.lse = lse; p.status = status;
+  p.osb = out_stride_b; p.osh = out_stride_h; p.osn = out_stride_n;
+  p.plan_slices = plan_slices; p.q_group = q_group; p.n_text = n_text;
+  p.B = B; p.H = H; p.N = N; p.nb = (N + 63) / 64; p.npairs = (p.nb + 1) / 2;
+  p.scale_log2 = sm_scale * 1.44269504f;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (D == 128)
+    return out_dtype == PARO_F16 ? launch_attn<128, __half>(q8, k8, v16, p, s)
+                                 : launch_attn<128, __nv_bfloat16>(q8, k8, v16, p, s);
+  return out_dtype == PARO_F16 ? launch_attn<64, __half>(q8, k8, v16, p, s)
+                               : launch_attn<64, __nv_bfloat16>(q8, k8, v16, p, s);
+}
+
+extern "C" int paro_status_poll(const int32_t* status, int32_t* host_out, paro_stream_t stream) {
+  PARO_REQUIRE(status, PARO_EINVAL, "paro_status_poll: null pointer");
+  int32_t w[4] = {0, 0, 0, 0};
+  PARO_CUDA_OK(cudaMemcpyAsync(w, status, sizeof(w), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+  PARO_CUDA_OK(cudaStreamSynchronize((cudaStream_t)stream));
+  if (host_out)
+    for (int i = 0; i < 4; ++i) host_out[i] = w[i];
+  if (w[0] != 0)
+    return fail(PARO_ETIMEOUT, "sparse attention wait expired: role %d, work item %d, tile %d", w[1], w[2], w[3]);
+  return PARO_OK;
+}

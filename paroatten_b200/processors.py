@@ -1,0 +1,164 @@
+"""diffusers attention processors with the reference's names, call signatures and attribute
+contract (paroattention/cogvideox.py:112-250, paroattention/wan.py:113-327).
+
+State injected by the pipeline set-up, exactly as the reference's `paroattn_convert` does
+(example/pipeline_cogvideox.py:120-136):
+    permute_plan  dict {'permute': [L,H] order ids, ...} (or a plan.PermutePlan)
+    sparse_mask   bool [T, L, H, nb, nb] (or a plan.SparsePlan)
+    i_block       layer index, i_timestep  timestep bin (set by TimestepCallback)
+    grid_fhw      latent grid (F, H, W); defaults to the reference's hard-coded 13x30x45 / 21x45x80
+The processors only need `attn` to expose to_q/to_k/to_v/to_out, norm_q/norm_k and heads, so
+they also work with any module of that shape.  Shapes are taken from the inputs (the reference
+hard-codes them at cogvideox.py:184 and wan.py:204).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import _lib
+from .core import paro_attention
+from .plan import PermutePlan, SparsePlan
+from .rope import RopeTables, rope_tables
+
+
+class _ProcessorBase:
+    default_grid = None
+    rope_family = None
+
+    def __init__(self):
+        self.time_accum = {"total": 0.0}
+        self.call_count = 0
+        self._pending = []
+        self.grid_fhw = self.default_grid
+        self.i_block = 0
+        self.i_timestep = 0
+        self.smooth_k = True
+        self._rope_cache = {}
+        self._pplan = None
+        self._splan = None
+
+    # -- plan handling ------------------------------------------------------------------------
+    def _plans(self, device):
+        if self._pplan is None or self._pplan_src is not self.permute_plan:
+            self._pplan_src = self.permute_plan
+            self._pplan = (self.permute_plan if isinstance(self.permute_plan, PermutePlan)
+                           else PermutePlan(self.permute_plan, self.grid_fhw, device))
+        src = getattr(self, "sparse_mask", None)
+        if src is None and hasattr(self, "prefetch_stream"):
+            src = self.prefetch_stream.sparse_mask  # the reference's CPU-resident mask holder
+        if src is None:
+            raise RuntimeError("processor has no sparse_mask")
+        if self._splan is None or self._splan_src is not src:
+            self._splan_src = src
+            self._splan = src if isinstance(src, SparsePlan) else SparsePlan(src, device)
+        return self._pplan, self._splan
+
+    def _rope(self, head_dim, device) -> RopeTables:
+        key = (head_dim, tuple(self.grid_fhw), str(device))
+        if key not in self._rope_cache:
+            self._rope_cache[key] = rope_tables(self.grid_fhw, head_dim, self.rope_family, device=device)
+        return self._rope_cache[key]
+
+    def _attend(self, query, key, value, n_text, use_rope):
+        """query/key/value: [B, N, H*D] projections; returns [B, N, H*D]."""
+        B, N, inner = query.shape
+        H = self._heads
+        D = inner // H
+        q, k, v = (t.view(B, N, H, D) for t in (query, key, value))
+        pplan, splan = self._plans(query.device)
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        out = paro_attention(q, k, v, pplan, splan, i_block=self.i_block, i_timestep=self.i_timestep,
+                             grid_fhw=self.grid_fhw, n_text=n_text,
+                             rope=self._rope(D, query.device) if use_rope else None,
+                             tensor_layout="NHD", smooth_k=self.smooth_k)
+        end.record()
+        self._pending.append((start, end))   # read lazily: no device sync per layer
+        self.call_count += 1
+        return out.reshape(B, N, inner)
+
+    def get_time_stats(self):
+        """Accumulated attention milliseconds (reference: cogvideox.py:247-250).  Events are
+        resolved here instead of synchronising the device after every layer (cogvideox.py:224)."""
+        if self._pending:
+            torch.cuda.synchronize()
+            for s, e in self._pending:
+                self.time_accum["total"] += s.elapsed_time(e)
+            self._pending.clear()
+        return {"total_ms": self.time_accum["total"]}
+
+
+class PARO_CogVideoXAttnProcessor2_0(_ProcessorBase):
+    """CogVideoX joint text+video self-attention (reference: cogvideox.py:112-250).  When
+    `image_rotary_emb` is given, the 3-D rotary embedding is applied inside the fused
+    RoPE+permute pass from tables built for `grid_fhw` (the passed tensor itself is not read)."""
+    default_grid = (13, 30, 45)
+    rope_family = "cogvideox"
+
+    def __call__(self, attn, hidden_states: torch.Tensor, encoder_hidden_states: torch.Tensor,
+                 attention_mask: Optional[torch.Tensor] = None,
+                 image_rotary_emb: Optional[torch.Tensor] = None) -> torch.Tensor:
+        text_seq_length = encoder_hidden_states.size(1)
+        hidden_states = torch.cat([encoder_hidden_states, hidden_states], dim=1)
+        self._heads = attn.heads
+        query, key, value = attn.to_q(hidden_states), attn.to_k(hidden_states), attn.to_v(hidden_states)
+        B, N, inner = key.shape
+        D = inner // attn.heads
+        if getattr(attn, "norm_q", None) is not None:
+            query = attn.norm_q(query.view(B, N, attn.heads, D)).reshape(B, N, inner)
+        if getattr(attn, "norm_k", None) is not None:
+            key = attn.norm_k(key.view(B, N, attn.heads, D)).reshape(B, N, inner)
+        hidden_states = self._attend(query, key, value, text_seq_length, image_rotary_emb is not None)
+        hidden_states = attn.to_out[0](hidden_states)
+        hidden_states = attn.to_out[1](hidden_states)
+        encoder_hidden_states, hidden_states = hidden_states.split(
+            [text_seq_length, hidden_states.size(1) - text_seq_length], dim=1)
+        return hidden_states, encoder_hidden_states
+
+
+class PARO_WanAttnProcessor2_0(_ProcessorBase):
+    """Wan2.1 self-attention (reference: wan.py:113-327, without its debugging detours at
+    :209-297).  Cross-attention layers keep the stock processor in the reference (wan.py:566) and
+    are not handled here."""
+    default_grid = (21, 45, 80)
+    rope_family = "wan"
+
+    def __call__(self, attn, hidden_states: torch.Tensor, encoder_hidden_states: Optional[torch.Tensor] = None,
+                 attention_mask: Optional[torch.Tensor] = None,
+                 rotary_emb: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if encoder_hidden_states is not None and encoder_hidden_states is not hidden_states:
+            raise ValueError("PARO_WanAttnProcessor2_0 handles self-attention only")
+        self._heads = attn.heads
+        query, key, value = attn.to_q(hidden_states), attn.to_k(hidden_states), attn.to_v(hidden_states)
+        if getattr(attn, "norm_q", None) is not None:
+            query = attn.norm_q(query)
+        if getattr(attn, "norm_k", None) is not None:
+            key = attn.norm_k(key)
+        hidden_states = self._attend(query, key, value, 0, rotary_emb is not None)
+        hidden_states = attn.to_out[0](hidden_states)
+        hidden_states = attn.to_out[1](hidden_states)
+        return hidden_states
+
+
+class TimestepCallback:
+    """Maps the denoising step to the sparse plan's timestep bin and pushes it into every
+    processor (reference: paroattention/prefetch_utils.py:4-32).  Duck-typed: no diffusers import."""
+    tensor_inputs = []
+
+    def __init__(self, num_timestep_for_sparse_mask: int = 10):
+        self.num_timestep_for_sparse_mask = num_timestep_for_sparse_mask
+        self.sparse_mask_timestep = 0
+
+    def on_step_end(self, pipeline, step, timestep, callback_kwargs):
+        total_steps = len(pipeline.scheduler.timesteps)
+        step = step % total_steps
+        normalized = (step + 1) / total_steps
+        self.sparse_mask_timestep = int(normalized * self.num_timestep_for_sparse_mask)
+        pipeline.transformer.i_timestep = self.sparse_mask_timestep
+        for block in pipeline.transformer.transformer_blocks:
+            block.attn1.processor.i_timestep = self.sparse_mask_timestep
+        return callback_kwargs
+
+    __call__ = on_step_end

@@ -1,0 +1,127 @@
+"""INT8 / FP8 quantisers with the reference's Python signatures (paroattention/quant.py)."""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import _lib
+
+_scratch = {}
+
+
+def _hnd(x: torch.Tensor, tensor_layout: str) -> torch.Tensor:
+    if tensor_layout == "HND":
+        v = x
+    elif tensor_layout == "NHD":
+        v = x.transpose(1, 2)
+    else:
+        raise ValueError(f"Unknown tensor layout: {tensor_layout}")
+    return v if v.stride(-1) == 1 else v.contiguous()
+
+
+def _stats_scratch(B, H, N, D, device) -> torch.Tensor:
+    need = _lib.lib().paro_channel_stats_scratch_bytes(B, H, N, D)
+    key = (device.index if device.index is not None else torch.cuda.current_device())
+    buf = _scratch.get(key)
+    if buf is None or buf.numel() < need:
+        buf = torch.empty(need, dtype=torch.uint8, device=device)
+        _scratch[key] = buf
+    return buf
+
+
+def channel_mean(x: torch.Tensor, tensor_layout: str = "HND", out_dtype=None) -> torch.Tensor:
+    """Mean over tokens -> [B,H,D] (the `km` argument of per_block_int8 / per_warp_int8);
+    deterministic fp64 accumulation.  out_dtype: x.dtype (default) or torch.float32."""
+    _lib.require_cuda(x)
+    xv = _hnd(x, tensor_layout)
+    B, H, N, D = xv.shape
+    f32 = out_dtype == torch.float32
+    with torch.cuda.device(x.device):
+        out = torch.empty(B, H, D, dtype=torch.float32 if f32 else x.dtype, device=x.device)
+        scr = _stats_scratch(B, H, N, D, x.device)
+        _lib.check(_lib.lib().paro_channel_mean(
+            xv.data_ptr(), _lib.dtype_code(x.dtype), B, H, N, D, xv.stride(0), xv.stride(1), xv.stride(2),
+            0 if f32 else out.data_ptr(), out.data_ptr() if f32 else 0, scr.data_ptr(), scr.numel(),
+            _lib.stream_ptr()))
+    return out
+
+
+def _quant_int8(x, tensor_layout, group, km=None, fold=0.0):
+    _lib.require_cuda(x, km)
+    xv = _hnd(x, tensor_layout)
+    B, H, N, D = xv.shape
+    nb = (N + 63) // 64
+    with torch.cuda.device(x.device):
+        out = torch.empty(B, H, N, D, dtype=torch.int8, device=x.device)
+        scale = torch.empty(B, H, nb * (64 // group), dtype=torch.float32, device=x.device)
+        if km is not None:
+            km = km.reshape(B, H, D).to(x.dtype).contiguous()
+        _lib.check(_lib.lib().paro_quant_int8(
+            xv.data_ptr(), _lib.dtype_code(x.dtype), B, H, N, D, xv.stride(0), xv.stride(1), xv.stride(2),
+            _lib.ptr(km), float(fold), group, out.data_ptr(), scale.data_ptr(), _lib.stream_ptr()))
+    if tensor_layout == "NHD":
+        out = out.transpose(1, 2)  # logical [B,N,H,D] view of the HND buffer
+    return out, scale
+
+
+def per_block_int8(q, k, km: Optional[torch.Tensor] = None, BLKQ: int = 128, BLKK: int = 64,
+                   sm_scale: Optional[float] = None, tensor_layout: str = "HND"):
+    """Reference signature paroattention/quant.py:22-103: Q per block with sm_scale*log2(e) folded
+    in, K per block (optionally mean-smoothed).  Only 64-token blocks are supported (the sparse
+    plan's granularity); the reference default BLKQ=128 is rejected."""
+    if BLKQ != 64 or BLKK != 64:
+        raise ValueError("paroatten_b200 quantises in 64-token blocks: pass BLKQ=64, BLKK=64")
+    D = q.shape[-1]
+    if sm_scale is None:
+        sm_scale = D ** -0.5
+    q8, qs = _quant_int8(q, tensor_layout, 64, fold=sm_scale * 1.44269504)
+    k8, ks = _quant_int8(k, tensor_layout, 64, km=km)
+    return q8, qs, k8, ks
+
+
+def per_warp_int8(q, k, km: Optional[torch.Tensor] = None, BLKQ: int = 128, WARPQ: int = 32, BLKK: int = 64,
+                  tensor_layout: str = "HND"):
+    """Reference signature paroattention/quant.py:105-180: Q per 32-row group (two scales per
+    64-token block), K per 64-token block (optionally mean-smoothed).  The processors call it
+    with BLKQ=64, WARPQ=32, BLKK=64 (cogvideox.py:186); that is the supported setting."""
+    if BLKQ != 64 or WARPQ != 32 or BLKK != 64:
+        raise ValueError("paroatten_b200 supports BLKQ=64, WARPQ=32, BLKK=64")
+    q8, qs = _quant_int8(q, tensor_layout, 32)
+    k8, ks = _quant_int8(k, tensor_layout, 64, km=km)
+    return q8, qs, k8, ks
+
+
+def sub_mean(v: torch.Tensor, tensor_layout: str = "HND"):
+    """Reference signature paroattention/quant.py:182-222: (v - mean over tokens) as fp16 and
+    the mean in v.dtype.  The mean comes from the deterministic reduction kernel; the
+    subtraction is one elementwise torch op (this helper is not on the attention path here:
+    V smoothing is part of per_channel_fp8)."""
+    vm = channel_mean(v, tensor_layout)
+    expand = vm.unsqueeze(2) if tensor_layout == "HND" else vm.unsqueeze(1)
+    return (v.float() - expand.float()).to(torch.float16), vm
+
+
+def per_channel_fp8(v: torch.Tensor, tensor_layout: str = "HND", scale_max: float = 448.0, smooth_v: bool = True,
+                    return_f16: bool = False):
+    """Reference signature paroattention/quant.py:224-293: V transposed to token-contiguous
+    [B,H,D,ceil64(N)] float8_e4m3fn (zero padded; no 16-token shuffle), per-channel scale
+    [B,H,D] and mean [B,H,D] (None without smoothing).  return_f16=True appends the same values
+    widened to fp16, which is what the attention kernel consumes."""
+    _lib.require_cuda(v)
+    vv = _hnd(v, tensor_layout)
+    B, H, N, D = vv.shape
+    npad = (N + 63) // 64 * 64
+    with torch.cuda.device(v.device):
+        v8 = torch.empty(B, H, D, npad, dtype=torch.float8_e4m3fn, device=v.device)
+        v16 = torch.empty(B, H, D, npad, dtype=torch.float16, device=v.device) if return_f16 else None
+        scale = torch.empty(B, H, D, dtype=torch.float32, device=v.device)
+        vm = torch.empty(B, H, D, dtype=torch.float32, device=v.device) if smooth_v else None
+        scr = _stats_scratch(B, H, N, D, v.device)
+        _lib.check(_lib.lib().paro_quant_v_fp8(
+            vv.data_ptr(), _lib.dtype_code(v.dtype), B, H, N, D, vv.stride(0), vv.stride(1), vv.stride(2),
+            int(bool(smooth_v)), float(scale_max), v8.data_ptr(), _lib.ptr(v16), scale.data_ptr(), _lib.ptr(vm),
+            scr.data_ptr(), scr.numel(), _lib.stream_ptr()))
+    if tensor_layout == "NHD":
+        v8 = v8.transpose(1, 2)  # [B,D,H,Npad] view, the reference's NHD output shape
+    return (v8, scale, vm, v16) if return_f16 else (v8, scale, vm)

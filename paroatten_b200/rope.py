@@ -1,0 +1,103 @@
+"""Fused 3D-RoPE + per-head token permutation (replaces paroattention._rope.rope_permutation,
+csrc/rope/rope.cu:14-48, and the torch loops permute_qk / permute_attn_out of
+paroattention/cogvideox.py:22-110)."""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+
+
+@dataclass
+class RopeTables:
+    """Per-axis angle tables [F+H+W, D/2]: row = axis base + coordinate, column = channel pair."""
+    mode: int            # _lib.ROPE_REAL_F32 or _lib.ROPE_COMPLEX_F64
+    cos: torch.Tensor
+    sin: torch.Tensor
+    pairs_f: int
+    pairs_h: int
+
+
+def axis_pairs(head_dim: int, family: str) -> Tuple[int, int, int]:
+    """Channel pairs rotated by the f / h / w coordinate: CogVideoX D/4, 3D/8, 3D/8 channels;
+    Wan h = w = 2*(D//6) channels, the rest for f (paroattention/wan.py:492-493)."""
+    if family == "cogvideox":
+        t, h = head_dim // 4, head_dim // 8 * 3
+        return t // 2, h // 2, h // 2
+    if family == "wan":
+        hw = 2 * (head_dim // 6)
+        return (head_dim - 2 * hw) // 2, hw // 2, hw // 2
+    raise ValueError(f"unknown rope family {family!r}")
+
+
+def rope_tables(grid, head_dim: int, family: str, theta: float = 10000.0, device="cuda") -> RopeTables:
+    """Angle of pair i of an axis with n pairs at coordinate p: p * theta^(-i/n).
+    fp32 tables and fp32 rotation for "cogvideox" (diffusers' real-valued apply_rotary_emb,
+    call site paroattention/cogvideox.py:167-172); fp64 for "wan" (wan.py:161-164,497-500)."""
+    F, H, W = (int(g) for g in grid)
+    pairs = axis_pairs(head_dim, family)
+    dt = torch.float32 if family == "cogvideox" else torch.float64
+    cos = torch.ones(F + H + W, head_dim // 2, dtype=dt)
+    sin = torch.zeros(F + H + W, head_dim // 2, dtype=dt)
+    row0 = col0 = 0
+    for n_pos, n_pair in zip((F, H, W), pairs):
+        dim = 2 * n_pair
+        freqs = 1.0 / (theta ** (torch.arange(0, dim, 2, dtype=dt)[:n_pair] / dim))
+        ang = torch.outer(torch.arange(n_pos, dtype=dt), freqs)
+        cos[row0:row0 + n_pos, col0:col0 + n_pair] = ang.cos()
+        sin[row0:row0 + n_pos, col0:col0 + n_pair] = ang.sin()
+        row0 += n_pos
+        col0 += n_pair
+    mode = _lib.ROPE_REAL_F32 if family == "cogvideox" else _lib.ROPE_COMPLEX_F64
+    return RopeTables(mode, cos.to(device).contiguous(), sin.to(device).contiguous(), pairs[0], pairs[1])
+
+
+def rope_permute(x: torch.Tensor, order_ids: Optional[torch.Tensor], grid, n_text: int = 0,
+                 rope: Optional[RopeTables] = None, inverse: bool = False,
+                 tensor_layout: str = "HND") -> torch.Tensor:
+    """One pass over x ([B,H,N,D], or [B,N,H,D] when tensor_layout="NHD"): optional RoPE on the
+    video tokens, then head h's tokens gathered in its axis order (`order_ids` int32 [H] on the
+    GPU; None = keep the order).  inverse=True undoes the permutation (no RoPE).
+    Returns a new contiguous [B,H,N,D] tensor."""
+    _lib.require_cuda(x, order_ids)
+    if tensor_layout == "NHD":
+        x = x.transpose(1, 2)
+    elif tensor_layout != "HND":
+        raise ValueError(f"Unknown tensor layout: {tensor_layout}")
+    B, H, N, D = x.shape
+    if x.stride(-1) != 1:
+        x = x.contiguous()
+    F, Hh, W = (int(g) for g in grid)
+    if order_ids is not None:
+        order_ids = order_ids.to(device=x.device, dtype=torch.int32).contiguous()
+        if order_ids.numel() != H:
+            raise ValueError("order_ids must hold one id per head")
+    with torch.cuda.device(x.device):
+        out = torch.empty(B, H, N, D, dtype=x.dtype, device=x.device)
+        r = rope
+        _lib.check(_lib.lib().paro_rope_permute(
+            x.data_ptr(), out.data_ptr(), _lib.dtype_code(x.dtype), B, H, N, D, x.stride(0), x.stride(1), x.stride(2),
+            int(n_text), F, Hh, W, _lib.ptr(order_ids), int(bool(inverse)),
+            r.mode if r is not None else _lib.ROPE_NONE, _lib.ptr(r.cos if r else None),
+            _lib.ptr(r.sin if r else None), r.pairs_f if r else 0, r.pairs_h if r else 0, _lib.stream_ptr()))
+    return out
+
+
+def rope_permutation(Q: torch.Tensor, K: torch.Tensor, freq, permutation: bool, *, order_ids=None, grid=None,
+                     n_text: int = 0):
+    """Same call shape as the reference op `_rope.rope_permutation(Q, K, freq, permutation) ->
+    (QO, KO)` (csrc/rope/rope.h:6).  `freq` is a RopeTables (the reference's position-independent
+    128-float table, rope.cuh:36-39, is a placeholder and has no meaning here).  Q, K are
+    [B,H,N,D]; with permutation=True each head is reordered by `order_ids` (default: id 1, the
+    H<->W swap the reference op performs, rope.cuh:41-50) over `grid` (default (1, H, W) is not
+    inferable from a flat token axis, so grid is required)."""
+    if grid is None:
+        raise ValueError("grid=(F,H,W) is required")
+    H = Q.shape[1]
+    ids = None
+    if permutation:
+        ids = order_ids if order_ids is not None else torch.full((H,), 1, dtype=torch.int32, device=Q.device)
+    return (rope_permute(Q, ids, grid, n_text, freq), rope_permute(K, ids, grid, n_text, freq))

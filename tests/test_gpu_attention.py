@@ -1,0 +1,191 @@
+"""Parity of the block-sparse attention kernel (and of the composed path) with the CPU
+fake-quant oracle.  Tolerance: cosine similarity >= 0.9995 and relative L1 <= 1e-2 per head."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import paroatten_b200 as pb
+from oracle import paro_oracle as po
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+DEV = "cuda"
+COS_MIN, RL1_MAX = 0.9995, 1e-2
+
+
+def assert_close(got, want, what=""):
+    c = po.cosine_per_head(got.cpu(), want).min().item()
+    r = po.rel_l1_per_head(got.cpu(), want).max().item()
+    assert c >= COS_MIN and r <= RL1_MAX, f"{what}: min cosine {c:.6f}, max rel-L1 {r:.3e}"
+
+
+def quantised(q, k, v, orders, grid, n_text=0):
+    qp, kp, vp = (po.permute_tokens(t, orders, grid, n_text) for t in (q, k, v))
+    km = po.channel_mean(kp, kp.dtype)
+    q8, qs = po.quant_int8(qp, 32)
+    k8, ks = po.quant_int8(kp, 64, km=km)
+    v8, vs, vm = po.quant_v_fp8(vp)
+    return q8, qs, k8, ks, v8, vs, vm
+
+
+@pytest.mark.parametrize("D,N,H,density,dtype", [
+    (64, 1024, 2, 0.5, torch.float16),
+    (128, 1024, 2, 0.5, torch.bfloat16),
+    (128, 64, 1, 1.0, torch.bfloat16),      # single block, odd block count
+    (64, 200, 3, 1.0, torch.float16),       # ragged tail 8, dense
+    (128, 1008, 2, 0.4, torch.bfloat16),    # tail 48
+    (128, 1016, 2, 0.4, torch.float16),     # tail 56, 16 blocks
+    (64, 976, 2, 0.3, torch.bfloat16),      # tail 16, odd block count (pair with a missing half)
+    (128, 4160, 2, 0.2, torch.bfloat16),    # 65 blocks: long lists, ring wrap-around
+])
+def test_kernel_on_oracle_quantised_operands(D, N, H, density, dtype):
+    """The kernel alone: operands quantised by the ORACLE, so only the attention differs."""
+    B = 2
+    q, k, v, _ = po.make_inputs(B, H, N, D, dtype, seed=N + D)
+    nb = (N + 63) // 64
+    mask = po.make_mask(H, nb, density, seed=N)
+    q8, qs, k8, ks, v8, vs, vm = quantised(q, k, v, [0] * H, (1, 1, N))
+    want, want_lse = po.sparse_attention(q8, qs, k8, ks, v8, vs, vm, mask, D ** -0.5, out_dtype=dtype, return_lse=True)
+    plan = pb.compact_plan(mask.to(DEV))
+    got, lse = pb.sparse_attn_quantized(q8.to(DEV), qs.to(DEV), k8.to(DEV), ks.to(DEV), v8.to(torch.float16).to(DEV),
+                                        vs.to(DEV), vm.to(DEV), plan, D ** -0.5, out_dtype=dtype, return_lse=True)
+    pb.check_status()
+    assert_close(got, want, f"D={D} N={N}")
+    assert (lse.cpu() - want_lse).abs().max().item() < 2e-3
+
+
+def test_c1_plumbing_fixture():
+    """BASELINE config 1 end to end against the committed oracle output."""
+    cfg = po.CONFIGS["c1_plumbing"]
+    N = 1024
+    q, k, v, orders = po.make_inputs(cfg["B"], cfg["H"], N, cfg["D"], cfg["dtype"], seed=0)
+    mask = po.make_mask(cfg["H"], 16, cfg["density"], seed=0)
+    g = np.load(os.path.join(GOLD, "c1_plumbing_out.npz"))
+    want = torch.from_numpy(g["out"]).view(torch.float16)
+    got, lse = pb.paro_attention(q.to(DEV), k.to(DEV), v.to(DEV), torch.tensor(orders), mask.to(DEV),
+                                 grid_fhw=cfg["grid"], return_lse=True)
+    pb.check_status()
+    assert_close(got, want, "c1")
+    assert (lse.cpu() - torch.from_numpy(g["lse"])).abs().max().item() < 2e-3
+
+
+@pytest.mark.parametrize("family,D,grid,n_text,dtype", [
+    ("cogvideox", 64, (3, 10, 15), 226, torch.bfloat16),
+    ("wan", 128, (3, 6, 13), 0, torch.bfloat16),
+    ("wan", 128, (2, 9, 8), 40, torch.float16),
+])
+def test_composed_path(family, D, grid, n_text, dtype):
+    """RoPE + reorder + quantisers + attention + inverse reorder, all on the GPU, against the
+    composed oracle; also checks the intermediate integer tensors bit for bit."""
+    B, H = 2, 6
+    N = n_text + grid[0] * grid[1] * grid[2]
+    q, k, v, orders = po.make_inputs(B, H, N, D, dtype, seed=sum(grid))
+    nb = (N + 63) // 64
+    mask = po.make_mask(H, nb, 0.4, seed=1, text_blocks=(n_text + 63) // 64)
+    cos, sin = po.rope_full_tables(grid, D, family)
+    kind = "real" if family == "cogvideox" else "complex"
+    want, want_lse = po.paro_attention(q, k, v, orders, mask, grid, n_text=n_text, rope=(kind, cos, sin), return_lse=True)
+    tabs = pb.rope_tables(grid, D, family)
+    got, lse = pb.paro_attention(q.to(DEV), k.to(DEV), v.to(DEV), {"permute": torch.tensor([orders])},
+                                 mask.to(DEV).reshape(1, 1, H, nb, nb), i_block=0, i_timestep=0, grid_fhw=grid,
+                                 n_text=n_text, rope=tabs, return_lse=True)
+    pb.check_status()
+    assert_close(got, want, family)
+    assert (lse.cpu() - want_lse).abs().max().item() < 2e-3
+    # NHD in, NHD out
+    got2 = pb.paro_attention(*(t.transpose(1, 2).contiguous().to(DEV) for t in (q, k, v)), torch.tensor(orders),
+                             mask.to(DEV), grid_fhw=grid, n_text=n_text, rope=tabs, tensor_layout="NHD")
+    assert torch.equal(got2.transpose(1, 2), got)
+
+
+def test_reference_operator_signature():
+    """paroattn_qk_int8_pv_fp16_cuda(q, k, v, sparse): already reordered inputs, bool mask."""
+    B, H, N, D = 2, 3, 520, 96   # head_dim padded to 128 like the reference
+    q, k, v, _ = po.make_inputs(B, H, N, D, torch.float16, seed=2)
+    nb = (N + 63) // 64
+    mask = po.make_mask(H, nb, 0.5, seed=2)
+    pad = lambda t: torch.nn.functional.pad(t, (0, 128 - D))
+    q8, qs = po.quant_int8(pad(q), 32)
+    k8, ks = po.quant_int8(pad(k), 64)
+    v8, vs, vm = po.quant_v_fp8(pad(v))
+    want = po.sparse_attention(q8, qs, k8, ks, v8, vs, vm, mask, D ** -0.5, out_dtype=torch.float16)[..., :D]
+    sparse = torch.stack([mask, mask]).to(DEV)  # [B,H,nb,nb] as the processors build it
+    got = pb.paroattn_qk_int8_pv_fp16_cuda(q.to(DEV), k.to(DEV), v.to(DEV), sparse)
+    pb.check_status()
+    assert got.shape == (B, H, N, D)
+    assert_close(got, want, "per_warp")
+    got_nhd = pb.paroattn(*(t.transpose(1, 2).contiguous().to(DEV) for t in (q, k, v)), tensor_layout="NHD", sparse=sparse)
+    assert torch.equal(got_nhd.transpose(1, 2), got)
+    # "per_thread": per-block Q with the scale folded in
+    q8b, qsb = po.quant_int8(pad(q), 64, fold_scale=D ** -0.5 * 1.44269504)
+    want_b = po.sparse_attention(q8b, qsb, k8, ks, v8, vs, vm, mask, 1.0 / 1.44269504, q_group=64,
+                                 out_dtype=torch.float16)[..., :D]
+    got_b = pb.paroattn_qk_int8_pv_fp16_cuda(q.to(DEV), k.to(DEV), v.to(DEV), sparse, qk_quant_gran="per_thread")
+    assert_close(got_b, want_b, "per_thread")
+    with pytest.raises(ValueError):
+        pb.paroattn_qk_int8_pv_fp16_cuda(q.to(DEV), k.to(DEV), v.to(DEV), sparse, is_causal=True)
+
+
+def test_dense_mask_matches_sdpa():
+    B, H, N, D = 1, 2, 1500, 128
+    q, k, v, _ = po.make_inputs(B, H, N, D, torch.bfloat16, seed=9)
+    mask = torch.ones(H, 24, 24, dtype=torch.bool, device=DEV)
+    got = pb.paroattn_qk_int8_pv_fp16_cuda(q.to(DEV), k.to(DEV), v.to(DEV), mask, smooth_k=True)
+    ref = torch.nn.functional.scaled_dot_product_attention(q.float(), k.float(), v.float())
+    assert po.cosine_per_head(got.cpu(), ref).min().item() > 0.998
+
+
+def test_empty_rows_give_zero():
+    B, H, N, D = 1, 1, 256, 64
+    q, k, v, _ = po.make_inputs(B, H, N, D, torch.float16, seed=3)
+    mask = torch.zeros(H, 4, 4, dtype=torch.bool)
+    mask[0, 0, 1] = mask[0, 3, 3] = True      # q-blocks 1 and 2 keep nothing
+    got = pb.paroattn_qk_int8_pv_fp16_cuda(q.to(DEV), k.to(DEV), v.to(DEV), mask.to(DEV))
+    pb.check_status()
+    assert (got[0, 0, 64:192] == 0).all() and got[0, 0, :64].abs().sum() > 0 and got[0, 0, 192:].abs().sum() > 0
+
+
+def test_processors_on_a_stand_in_attention_module():
+    """The two processors driven by a minimal module with the attributes they read."""
+    import torch.nn as nn
+
+    class Attn(nn.Module):
+        def __init__(self, dim, heads):
+            super().__init__()
+            self.heads = heads
+            self.to_q, self.to_k, self.to_v = (nn.Linear(dim, dim) for _ in range(3))
+            self.to_out = nn.ModuleList([nn.Linear(dim, dim), nn.Dropout(0.0)])
+            self.norm_q = self.norm_k = None
+
+    torch.manual_seed(0)
+    heads, D, grid, n_text = 2, 64, (2, 4, 8), 32
+    attn = Attn(heads * D, heads).to(DEV, torch.bfloat16)
+    proc = pb.PARO_CogVideoXAttnProcessor2_0()
+    proc.grid_fhw = grid
+    proc.permute_plan = {"permute": torch.tensor([[4, 2]])}
+    nb = (n_text + 64 + 63) // 64
+    proc.sparse_mask = torch.ones(1, 1, heads, nb, nb, dtype=torch.bool, device=DEV)
+    proc.i_block, proc.i_timestep = 0, 0
+    hs = torch.randn(1, 64, heads * D, device=DEV, dtype=torch.bfloat16)
+    enc = torch.randn(1, n_text, heads * D, device=DEV, dtype=torch.bfloat16)
+    h_out, e_out = proc(attn, hs, enc, image_rotary_emb=None)
+    assert h_out.shape == hs.shape and e_out.shape == enc.shape
+    x = torch.cat([enc, hs], 1)
+    qkv = [f(x).view(1, -1, heads, D).transpose(1, 2).float() for f in (attn.to_q, attn.to_k, attn.to_v)]
+    ref = torch.nn.functional.scaled_dot_product_attention(*qkv).transpose(1, 2).reshape(1, -1, heads * D)
+    ref = attn.to_out[0](ref.to(torch.bfloat16))
+    got = torch.cat([e_out, h_out], 1)
+    assert torch.nn.functional.cosine_similarity(got.float().flatten(), ref.float().flatten(), dim=0) > 0.99
+    assert proc.get_time_stats()["total_ms"] > 0 and proc.call_count == 1
+
+    wan = pb.PARO_WanAttnProcessor2_0()
+    wan.grid_fhw = (2, 4, 12)
+    wan.permute_plan = {"permute": torch.tensor([[1, 5]])}
+    wan.sparse_mask = torch.ones(1, 1, heads, 2, 2, dtype=torch.bool, device=DEV)
+    hs = torch.randn(1, 96, heads * D, device=DEV, dtype=torch.bfloat16)
+    out = wan(attn, hs, rotary_emb=None)
+    qkv = [f(hs).view(1, -1, heads, D).transpose(1, 2).float() for f in (attn.to_q, attn.to_k, attn.to_v)]
+    ref = attn.to_out[0](torch.nn.functional.scaled_dot_product_attention(*qkv).transpose(1, 2).reshape(1, -1, heads * D).to(torch.bfloat16))
+    assert torch.nn.functional.cosine_similarity(out.float().flatten(), ref.float().flatten(), dim=0) > 0.99
