@@ -214,7 +214,6 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     const float rowscale = (tok < p.N ? p.q_scale[(size_t)bh * per_bh + tok / p.q_group] : 0.f) * p.scale_log2;
     float m = -INFINITY, l = 0.f;
     bool ok = true;
-
     for (int i = 0; i < n_ent; ++i) {
       const int e = ent[i];
       const int kb = e >> 2;
@@ -223,6 +222,16 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       if (!ok) {
         report_timeout(p, abort_flag, 6, i);
         break;
+      }
+      // A parity wait can only tell "the phase before the current one is over", so every thread
+      // consumes every completion of the P.V barrier in order: P.V of tile i-1 here (it was issued
+      // before this tile's scores were ready, so this costs nothing), the last one in the epilogue.
+      if (i > 0) {
+        ok = __all_sync(0xffffffffu, mbar_wait_bounded(bar_pvdone, (i - 1) & 1, abort_flag, WAIT_LIMIT));
+        if (!ok) {
+          report_timeout(p, abort_flag, 7, i);
+          break;
+        }
       }
       tc_fence_after();
       uint32_t pk[32];
@@ -246,14 +255,7 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           m = mx;
           l *= alpha;
         }
-        if (__any_sync(0xffffffffu, resc)) {
-          // O may only be touched once the previous P.V has landed
-          ok = __all_sync(0xffffffffu, mbar_wait_bounded(bar_pvdone, (i - 1) & 1, abort_flag, WAIT_LIMIT));
-          if (!ok) {
-            report_timeout(p, abort_flag, 7, i);
-            break;
-          }
-          tc_fence_after();
+        if (__any_sync(0xffffffffu, resc)) {  // the previous P.V has landed (waited above): O may be touched
 #pragma unroll
           for (int c = 0; c < D / 32; ++c) {
             uint32_t o[32];
