@@ -40,6 +40,8 @@ enum { PARO_ROPE_NONE = 0, PARO_ROPE_REAL_F32 = 1, PARO_ROPE_COMPLEX_F64 = 2 };
 
 int paro_version(void);
 const char* paro_last_error(void);
+/* Number of kernels this library has launched in this process so far. */
+long long paro_launch_count(void);
 
 /* ---- token permutation --------------------------------------------------------------- */
 

@@ -63,6 +63,7 @@ _i32, _i64, _f32, _vp, _sz = ctypes.c_int, ctypes.c_int64, ctypes.c_float, ctype
 SIGNATURES = {
     "paro_version": (ctypes.c_int, []),
     "paro_last_error": (ctypes.c_char_p, []),
+    "paro_launch_count": (ctypes.c_longlong, []),
     "paro_build_perm_index": (_i32, [_vp, _i32, _i32, _i32, _i32, _vp, _vp]),
     "paro_rope_permute": (_i32, [_vp, _vp, _i32, _i32, _i32, _i32, _i32, _i64, _i64, _i64, _i32, _i32, _i32, _i32,
                                  _vp, _i32, _i32, _vp, _vp, _i32, _i32, _vp]),

@@ -12,6 +12,14 @@ from .quant import _hnd, channel_mean, per_channel_fp8, per_warp_int8, per_block
 from .rope import RopeTables, rope_permute
 
 _status = {}
+_timing_sink = None  # optional list receiving (start, end) CUDA events around each attention launch
+
+
+def set_attention_timing(sink) -> None:
+    """Pass a list to have every attention launch bracketed by CUDA events on the launching
+    stream (appended as (start, end) pairs); pass None to switch it off."""
+    global _timing_sink
+    _timing_sink = sink
 
 
 def _status_words(device: torch.device) -> torch.Tensor:
@@ -64,12 +72,19 @@ def sparse_attn_quantized(q_int8, q_scale, k_int8, k_scale, v_f16, v_scale, vm, 
         if tuple(ov.shape) != (B, H, N, D) or ov.stride(-1) != 1:
             raise ValueError("out has the wrong shape or a strided last dimension")
         lse = torch.empty(B, H, N, dtype=torch.float32, device=dev) if return_lse else None
+        sink = _timing_sink
+        if sink is not None:
+            ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+            ev[0].record()
         _lib.check(_lib.lib().paro_sparse_attn(
             q_int8.data_ptr(), k_int8.data_ptr(), v_f16.data_ptr(), q_scale.data_ptr(), int(q_group),
             k_scale.data_ptr(), v_scale.data_ptr(), _lib.ptr(vm), plan.pair_ptr.data_ptr(), plan.pair_ent.data_ptr(),
             plan.slices, _lib.ptr(inv_index), int(n_text), out.data_ptr(), _lib.dtype_code(out.dtype),
             ov.stride(0), ov.stride(1), ov.stride(2), _lib.ptr(lse), B, H, N, D, float(sm_scale),
             _status_words(dev).data_ptr(), _lib.stream_ptr()))
+        if sink is not None:
+            ev[1].record()
+            sink.append(ev)
     return (out, lse) if return_lse else out
 
 

@@ -1,6 +1,12 @@
 #include "common.cuh"
 
+#include <atomic>
+
 namespace paro {
+
+static std::atomic<long long> g_launches{0};
+void count_launches(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+long long launches() { return g_launches.load(std::memory_order_relaxed); }
 
 char* error_buffer() {
   static thread_local char buf[512] = "";
@@ -31,4 +37,5 @@ int check_tensor(const char* name, const void* p, int dtype, int B, int H, int N
 }  // namespace paro
 
 extern "C" int paro_version(void) { return 100; }
+extern "C" long long paro_launch_count(void) { return paro::launches(); }
 extern "C" const char* paro_last_error(void) { return paro::error_buffer(); }

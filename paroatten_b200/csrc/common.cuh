@@ -27,7 +27,12 @@ int fail(int code, const char* fmt, ...);
     if (!(cond)) return ::paro::fail(code, __VA_ARGS__); \
   } while (0)
 
-inline int check_launch(const char* what) {
+// Process-wide count of kernels this library has launched (read by paro_launch_count()).
+void count_launches(int n);
+long long launches();
+
+inline int check_launch(const char* what, int n_kernels = 1) {
+  count_launches(n_kernels);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail(PARO_ECUDA, "%s launch: %s", what, cudaGetErrorString(e));
   return PARO_OK;

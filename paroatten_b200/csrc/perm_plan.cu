@@ -118,7 +118,7 @@ extern "C" int paro_plan_count(const uint8_t* mask, int slices, int nbq, int nbk
   plan_count_kernel<true><<<min(4096, (prow + 7) / 8), 256, 0, s>>>(mask, slices, nbq, nbk, npairs, pair_ptr);
   scan_kernel<<<1, 1024, 0, s>>>(row_ptr, rows);
   scan_kernel<<<1, 1024, 0, s>>>(pair_ptr, prow);
-  return check_launch("plan_count");
+  return check_launch("plan_count", 4);
 }
 
 extern "C" int paro_plan_fill(const uint8_t* mask, int slices, int nbq, int nbk,
@@ -138,5 +138,5 @@ extern "C" int paro_plan_fill(const uint8_t* mask, int slices, int nbq, int nbk,
   if (pair_cap > 0)
     plan_fill_kernel<true><<<min(4096, (prow + 7) / 8), 256, 0, s>>>(mask, slices, nbq, nbk, npairs, pair_ptr,
                                                                      pair_ent, pair_cap);
-  return check_launch("plan_fill");
+  return check_launch("plan_fill", (cols_cap > 0) + (pair_cap > 0));
 }

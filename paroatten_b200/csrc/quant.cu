@@ -287,7 +287,7 @@ extern "C" int paro_channel_mean(const void* x, int dtype, int B, int H, int N, 
                                                                (__nv_bfloat16*)mean_out, mean_f32, nullptr, nullptr,
                                                                nullptr);
   }
-  return check_launch("channel_mean");
+  return check_launch("channel_mean", 2);
 }
 
 namespace {
@@ -342,7 +342,7 @@ int run_v_fp8(const void* v, int B, int H, int N, int D, int64_t sb, int64_t sh,
   else
     quant_v_fp8_kernel<T, 64><<<grid, 256, 0, s>>>((const T*)v, H, N, npad, sb, sh, sn, inv_tab, mean_tab, v8,
                                                    (__half*)v16);
-  return check_launch("quant_v_fp8");
+  return check_launch("quant_v_fp8", 3);
 }
 }  // namespace
 
