@@ -64,6 +64,31 @@ __device__ __forceinline__ float ex2_approx(float x) {
   return y;
 }
 
+// Packed pairs of fp32 (sm_100a has 2-wide fp32 FMA / ADD).
+__device__ __forceinline__ uint64_t pack2(float a, float b) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t r, float& a, float& b) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(r));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+
 __device__ __forceinline__ void report_timeout(const AttnParams& p, volatile int* abort_flag, int where, int iter) {
   if (atomicCAS(p.status, 0, PARO_ETIMEOUT) == 0) {
     p.status[1] = where;
@@ -242,11 +267,26 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         tmem_wait_ld();
         const int valid = min(64, p.N - kb * 64);
         const float sc = rowscale * p.k_scale[(size_t)bh * p.nb + kb];
-        int imax = INT_MIN;
+        // int32 scores -> fp32 (exact: |s| < 2^24); columns past the end of the sequence become -inf
+        float f[64];
 #pragma unroll
-        for (int j = 0; j < 64; ++j)
-          if (j < valid) imax = max(imax, (int)s[j]);
-        const float mx = (float)imax * sc;
+        for (int j = 0; j < 64; ++j) f[j] = (float)(int)s[j];
+        if (valid < 64) {
+#pragma unroll
+          for (int j = 0; j < 64; ++j)
+            if (j >= valid) f[j] = -INFINITY;
+        }
+        float mx4[4] = {f[0], f[1], f[2], f[3]};   // four independent chains of 3-input max
+#pragma unroll
+        for (int j = 4; j < 64; j += 8) {
+          mx4[0] = max3(mx4[0], f[j], f[j + 1]);
+          mx4[1] = max3(mx4[1], f[j + 2], f[j + 3]);
+          if (j + 4 < 64) {
+            mx4[2] = max3(mx4[2], f[j + 4], f[j + 5]);
+            mx4[3] = max3(mx4[3], f[j + 6], f[j + 7]);
+          }
+        }
+        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sc;
         float alpha = 1.f;
         bool resc = false;
         if (mx > m + RESCALE_TAU) {
@@ -267,18 +307,20 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           }
           tmem_wait_st();
         }
-        const float negm = -m;
-        float sum = 0.f;
+        const uint64_t sc2 = pack2(sc, sc), negm2 = pack2(-m, -m);
+        uint64_t sum2[2] = {0ull, 0ull};
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
-          float p0 = ex2_approx(fmaf((float)(int)s[2 * j], sc, negm));
-          float p1 = ex2_approx(fmaf((float)(int)s[2 * j + 1], sc, negm));
-          if (2 * j >= valid) p0 = 0.f;
-          if (2 * j + 1 >= valid) p1 = 0.f;
-          sum += p0 + p1;
+          float x0, x1;
+          unpack2(fma2(pack2(f[2 * j], f[2 * j + 1]), sc2, negm2), x0, x1);
+          const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);   // 2^-inf = 0 for masked columns
+          sum2[j & 1] = add2(sum2[j & 1], pack2(p0, p1));
           const __half2 h2 = __floats2half2_rn(p0, p1);
           pk[j] = *reinterpret_cast<const uint32_t*>(&h2);
         }
+        float sa, sb;
+        unpack2(add2(sum2[0], sum2[1]), sa, sb);
+        const float sum = sa + sb;
         l += sum;
       } else {
 #pragma unroll
