@@ -4,12 +4,14 @@
 // tile -- the native tcgen05.mma M -- walking the union of the two blocks' kept k-blocks.  Each list
 // entry says which of the two halves keeps the block; the half that does not is given P = 0.
 //
-//   warp 0     TMA producer: Q tile once, then K (int8) and V^T (fp16) tiles through a ring
-//   warp 1     owns TMEM; one lane issues S = Q.K^T (kind::i8, int32 accumulators in TMEM) and
-//              O += P.V (kind::f16, P read from TMEM, fp32 accumulators in TMEM)
-//   warps 2-5  one thread per q row: online softmax in fp32 (base 2, lazy rescaling), P written
+//   warps 0-3  one thread per q row: online softmax in fp32 (base 2, lazy rescaling), P written
 //              back over S in TMEM as fp16, epilogue O/l * v_scale + vm stored to the row's
-//              un-permuted position.
+//              un-permuted position.  This warpgroup takes the registers the others give up.
+//   warp 4     TMA producer for Q (once) and the K ring (int8 tiles, freed as soon as Q.K^T is done)
+//   warp 5     TMA producer for the V^T ring (fp16 tiles, freed when P.V is done)
+//   warp 6     owns TMEM; one lane issues S = Q.K^T (kind::i8, int32 accumulators in TMEM) and
+//              O += P.V (kind::f16, P read from TMEM, fp32 accumulators in TMEM)
+//   warp 7     idle (completes the second warpgroup)
 //
 // S is double buffered so that QK^T of tile i+1 overlaps the softmax of tile i; two CTAs share an
 // SM so that one CTA's softmax overlaps the other's MMAs.  Every wait is bounded: on expiry the
@@ -26,17 +28,23 @@ namespace paro {
 
 using namespace umma;
 
-constexpr int ATT_THREADS = 192;
+constexpr int ATT_THREADS = 256;
 constexpr int TMEM_COLS = 256;              // S0 [0,64) S1 [64,128) O [128,128+D)
 constexpr long long WAIT_LIMIT = 400000000; // SM cycles (~0.2 s) before a wait gives up
 constexpr float RESCALE_TAU = 8.0f;         // rescale O only when the row max grows by > 2^8
 
 template <int D> struct AttnCfg {
-  static constexpr int STAGES = (D == 128) ? 3 : 6;   // sized so that exactly two CTAs fit an SM
+  // ring depths, sized so that exactly two CTAs fit an SM (TMEM allows no more)
+#ifndef PARO_ATT_KST128
+#define PARO_ATT_KST128 5
+#define PARO_ATT_VST128 3
+#endif
+  static constexpr int K_STAGES = (D == 128) ? PARO_ATT_KST128 : 8;
+  static constexpr int V_STAGES = (D == 128) ? PARO_ATT_VST128 : 6;
   static constexpr int Q_BYTES = 128 * D;
   static constexpr int K_BYTES = 64 * D;
   static constexpr int V_BYTES = D * 128;   // D rows of 64 fp16
-  static constexpr int TILE_BYTES = Q_BYTES + STAGES * (K_BYTES + V_BYTES);
+  static constexpr int TILE_BYTES = Q_BYTES + K_STAGES * K_BYTES + V_STAGES * V_BYTES;
   static constexpr int AUX_BYTES = 2048;    // barriers, TMEM pointer, abort flag, v_scale, vm
   static constexpr int SMEM_BYTES = TILE_BYTES + AUX_BYTES + 1024 /* alignment slack */;
 };
@@ -98,6 +106,18 @@ __device__ __forceinline__ void report_timeout(const AttnParams& p, volatile int
   *abort_flag = 1;
 }
 
+// Optional cycle accounting of the roles (diagnostic builds only: -DPARO_ATTN_TRACE).
+#ifdef PARO_ATTN_TRACE
+__device__ unsigned long long g_trace[16];
+#define TRACE_DECL(cond) const bool tr_on = (cond); long long tr_t = clock64()
+#define TRACE_LAP(slot) do { if (tr_on) { const long long now__ = clock64(); atomicAdd(&g_trace[slot], (unsigned long long)(now__ - tr_t)); tr_t = now__; } } while (0)
+#define TRACE_COUNT(slot, n) do { if (tr_on) atomicAdd(&g_trace[slot], (unsigned long long)(n)); } while (0)
+#else
+#define TRACE_DECL(cond) do { } while (0)
+#define TRACE_LAP(slot) do { } while (0)
+#define TRACE_COUNT(slot, n) do { } while (0)
+#endif
+
 #define ATT_WAIT(bar, parity, where, iter)                                   \
   if (!mbar_wait_bounded((bar), (parity), abort_flag, WAIT_LIMIT)) {         \
     report_timeout(p, abort_flag, (where), (iter));                          \
@@ -109,28 +129,29 @@ __global__ void __launch_bounds__(ATT_THREADS, 2)
 sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                    const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
   using Cfg = AttnCfg<D>;
-  constexpr int NST = Cfg::STAGES;
+  constexpr int KST = Cfg::K_STAGES, VST = Cfg::V_STAGES;
   if (*reinterpret_cast<volatile int32_t*>(p.status) != 0) return;  // an earlier CTA failed: drain quickly
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;
   uint8_t* sK = sQ + Cfg::Q_BYTES;
-  uint8_t* sV = sK + NST * Cfg::K_BYTES;
+  uint8_t* sV = sK + KST * Cfg::K_BYTES;
   uint8_t* aux = smem + Cfg::TILE_BYTES;
   uint64_t* bar_q = reinterpret_cast<uint64_t*>(aux);   // [1]
-  uint64_t* bar_kfull = bar_q + 1;                      // [NST]
-  uint64_t* bar_vfull = bar_kfull + NST;                // [NST]
-  uint64_t* bar_empty = bar_vfull + NST;                // [NST]
-  uint64_t* bar_sfull = bar_empty + NST;                // [2]
+  uint64_t* bar_kfull = bar_q + 1;                      // [KST]
+  uint64_t* bar_kempty = bar_kfull + KST;               // [KST]
+  uint64_t* bar_vfull = bar_kempty + KST;               // [VST]
+  uint64_t* bar_vempty = bar_vfull + VST;               // [VST]
+  uint64_t* bar_sfull = bar_vempty + VST;               // [2]
   uint64_t* bar_pready = bar_sfull + 2;                 // [2]
   uint64_t* bar_pvdone = bar_pready + 2;                // [1]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_pvdone + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  float* s_vscale = reinterpret_cast<float*>(aux + 256);
+  float* s_vscale = reinterpret_cast<float*>(aux + 512);
   float* s_vm = s_vscale + D;
-  static_assert(256 + 2 * D * 4 <= Cfg::AUX_BYTES, "aux area too small");
-  static_assert((6 + 3 * NST) * 8 + 8 <= 256, "barrier area too small");
+  static_assert(512 + 2 * D * 4 <= Cfg::AUX_BYTES, "aux area too small");
+  static_assert((6 + 2 * KST + 2 * VST) * 8 + 8 <= 512, "barrier area too small");
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int bh = blockIdx.x / p.npairs, pair = blockIdx.x % p.npairs;
@@ -141,10 +162,13 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 
   if (threadIdx.x == 0) {
     mbar_init(bar_q, 1);
-    for (int i = 0; i < NST; ++i) {
+    for (int i = 0; i < KST; ++i) {
       mbar_init(bar_kfull + i, 1);
+      mbar_init(bar_kempty + i, 1);
+    }
+    for (int i = 0; i < VST; ++i) {
       mbar_init(bar_vfull + i, 1);
-      mbar_init(bar_empty + i, 1);
+      mbar_init(bar_vempty + i, 1);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar_sfull + i, 1);
@@ -154,7 +178,7 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     *abort_flag = 0;
     fence_barrier_init();
   }
-  if (warp == 1) {
+  if (warp == 6) {
     tmem_alloc(tmem_slot, TMEM_COLS);
     tmem_relinquish();
   }
@@ -165,36 +189,56 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   const uint32_t tS[2] = {tmem_base, tmem_base + 64u};
   const uint32_t tO = tmem_base + 128u;
 
-  if (warp == 0) {
-    // ------------------------------------------------------------------ TMA producer
+  if (warp >= 4) asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+  if (warp == 4) {
+    // ------------------------------------------------------------------ TMA producer: Q, K ring
     if (lane == 0) {
       tma_prefetch_desc(&tm_q);
       tma_prefetch_desc(&tm_k);
-      tma_prefetch_desc(&tm_v);
       mbar_arrive_expect_tx(bar_q, Cfg::Q_BYTES);
       tma_load_3d(sQ, &tm_q, 0, pair * 128, bh, bar_q);
+      TRACE_DECL(true);
       for (int i = 0; i < n_ent; ++i) {
-        const int st = i % NST, use = i / NST;
-        if (use > 0) { ATT_WAIT(bar_empty + st, (use - 1) & 1, 1, i) }
+        const int st = i % KST, use = i / KST;
         const int kb = ent[i] >> 2;
+        TRACE_LAP(15);
+        if (use > 0) { ATT_WAIT(bar_kempty + st, (use - 1) & 1, 1, i) }
+        TRACE_LAP(14);
+#ifdef PARO_ABL_NO_TMA
+        if (use > 0) { mbar_arrive(bar_kfull + st); continue; }
+#endif
         mbar_arrive_expect_tx(bar_kfull + st, Cfg::K_BYTES);
         tma_load_3d(sK + st * Cfg::K_BYTES, &tm_k, 0, kb * 64, bh, bar_kfull + st);
+      }
+    }
+  } else if (warp == 5) {
+    // ------------------------------------------------------------------ TMA producer: V ring
+    if (lane == 0) {
+      tma_prefetch_desc(&tm_v);
+      for (int i = 0; i < n_ent; ++i) {
+        const int st = i % VST, use = i / VST;
+        const int kb = ent[i] >> 2;
+        if (use > 0) { ATT_WAIT(bar_vempty + st, (use - 1) & 1, 9, i) }
+#ifdef PARO_ABL_NO_TMA
+        if (use > 0) { mbar_arrive(bar_vfull + st); continue; }
+#endif
         mbar_arrive_expect_tx(bar_vfull + st, Cfg::V_BYTES);
         tma_load_3d(sV + st * Cfg::V_BYTES, &tm_v, kb * 64, 0, bh, bar_vfull + st);
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == 6) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t IDESC_QK = instr_desc(2, 1, 1, 128, 64);  // s32 += s8 * s8
       constexpr uint32_t IDESC_PV = instr_desc(1, 0, 0, 128, D);   // f32 += f16 * f16
       const uint64_t dQ = smem_desc(smem_u32(sQ), D);
       auto issue_qk = [&](int i) {
-        const uint64_t dK = smem_desc(smem_u32(sK + (i % NST) * Cfg::K_BYTES), D);
+        const uint64_t dK = smem_desc(smem_u32(sK + (i % KST) * Cfg::K_BYTES), D);
 #pragma unroll
         for (int k = 0; k < D / 32; ++k)
           mma_i8_ss(tS[i & 1], desc_advance(dQ, 32 * k), desc_advance(dK, 32 * k), IDESC_QK, k > 0);
         mma_commit(bar_sfull + (i & 1));
+        mma_commit(bar_kempty + i % KST);
       };
       do {
         ATT_WAIT(bar_q, 0, 2, -1)
@@ -202,32 +246,39 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         ATT_WAIT(bar_kfull + 0, 0, 3, 0)
         tc_fence_after();
         issue_qk(0);
+        TRACE_DECL(true);
         for (int i = 0; i < n_ent; ++i) {
-          const int st = i % NST;
+          const int st = i % VST;
+          TRACE_LAP(10);
           if (i + 1 < n_ent) {
-            ATT_WAIT(bar_kfull + (i + 1) % NST, ((i + 1) / NST) & 1, 3, i + 1)
+            ATT_WAIT(bar_kfull + (i + 1) % KST, ((i + 1) / KST) & 1, 3, i + 1)
+            TRACE_LAP(11);
             tc_fence_after();
             issue_qk(i + 1);
           }
+          TRACE_LAP(10);
           ATT_WAIT(bar_pready + (i & 1), (i >> 1) & 1, 4, i)
-          ATT_WAIT(bar_vfull + st, (i / NST) & 1, 5, i)
+          TRACE_LAP(12);
+          ATT_WAIT(bar_vfull + st, (i / VST) & 1, 5, i)
+          TRACE_LAP(13);
           tc_fence_after();
           const uint64_t dV = smem_desc(smem_u32(sV + st * Cfg::V_BYTES), 128);
 #pragma unroll
           for (int k = 0; k < 4; ++k)
             mma_f16_ts(tO, tS[i & 1] + 8 * k, desc_advance(dV, 32 * k), IDESC_PV, (i > 0 || k > 0) ? 1u : 0u);
-          mma_commit(bar_empty + st);
+          mma_commit(bar_vempty + st);
           mma_commit(bar_pvdone);
         }
       } while (false);
     }
-  } else {
+  } else if (warp < 4) {
     // ------------------------------------------------------------------ softmax + epilogue
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 200;");
     const int qd = warp & 3;                 // TMEM lane quadrant this warp may touch
     const int r = qd * 32 + lane;            // row inside the 128-row tile
     const int half = qd >> 1;                // which q-block of the pair
     const uint32_t lane_off = (uint32_t)(qd * 32) << 16;
-    const int tid = threadIdx.x - 64;
+    const int tid = threadIdx.x;
     if (tid < D) {
       s_vscale[tid] = p.v_scale[(size_t)bh * D + tid];
       s_vm[tid] = p.vm ? p.vm[(size_t)bh * D + tid] : 0.f;
@@ -239,15 +290,27 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     const float rowscale = (tok < p.N ? p.q_scale[(size_t)bh * per_bh + tok / p.q_group] : 0.f) * p.scale_log2;
     float m = -INFINITY, l = 0.f;
     bool ok = true;
+    TRACE_DECL(warp == 0 && lane == 0);
+    TRACE_COUNT(9, n_ent);
+    const float* kscale_bh = p.k_scale + (size_t)bh * p.nb;
+    int e_next = n_ent > 0 ? ent[0] : 0;
+    float ks_next = n_ent > 0 ? kscale_bh[e_next >> 2] : 0.f;
     for (int i = 0; i < n_ent; ++i) {
-      const int e = ent[i];
+      const int e = e_next;
+      const float kscale = ks_next;
       const int kb = e >> 2;
       const bool keep = (e >> half) & 1;
+      if (i + 1 < n_ent) {   // fetched one tile ahead so that the loads are off the critical path
+        e_next = ent[i + 1];
+        ks_next = kscale_bh[e_next >> 2];
+      }
+      TRACE_LAP(0);
       ok = __all_sync(0xffffffffu, mbar_wait_bounded(bar_sfull + (i & 1), (i >> 1) & 1, abort_flag, WAIT_LIMIT));
       if (!ok) {
         report_timeout(p, abort_flag, 6, i);
         break;
       }
+      TRACE_LAP(1);
       // A parity wait can only tell "the phase before the current one is over", so every thread
       // consumes every completion of the P.V barrier in order: P.V of tile i-1 here (it was issued
       // before this tile's scores were ready, so this costs nothing), the last one in the epilogue.
@@ -259,14 +322,21 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         }
       }
       tc_fence_after();
+      TRACE_LAP(2);
       uint32_t pk[32];
+#ifdef PARO_ABL_NO_EXP
+      if (false) {
+#else
       if (keep) {
+#endif
+        TRACE_COUNT(8, 1);
         uint32_t s[64];
         tmem_ld32(tS[i & 1] + lane_off, s);
         tmem_ld32(tS[i & 1] + lane_off + 32, s + 32);
         tmem_wait_ld();
+        TRACE_LAP(3);
         const int valid = min(64, p.N - kb * 64);
-        const float sc = rowscale * p.k_scale[(size_t)bh * p.nb + kb];
+        const float sc = rowscale * kscale;
         // int32 scores -> fp32 (exact: |s| < 2^24); columns past the end of the sequence become -inf
         float f[64];
 #pragma unroll
@@ -287,6 +357,7 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           }
         }
         const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sc;
+        TRACE_LAP(4);
         float alpha = 1.f;
         bool resc = false;
         if (mx > m + RESCALE_TAU) {
@@ -307,6 +378,7 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           }
           tmem_wait_st();
         }
+        TRACE_LAP(5);
         const uint64_t sc2 = pack2(sc, sc), negm2 = pack2(-m, -m);
         uint64_t sum2[2] = {0ull, 0ull};
 #pragma unroll
@@ -322,6 +394,7 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         unpack2(add2(sum2[0], sum2[1]), sa, sb);
         const float sum = sa + sb;
         l += sum;
+        TRACE_LAP(6);
       } else {
 #pragma unroll
         for (int j = 0; j < 32; ++j) pk[j] = 0u;
@@ -330,6 +403,7 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(bar_pready + (i & 1));
+      TRACE_LAP(7);
     }
 
     // epilogue (the TMEM loads are warp-collective: every lane of the warp executes them, rows past
@@ -378,7 +452,7 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) {
+  if (warp == 6) {
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
@@ -478,6 +552,17 @@ extern "C" int paro_sparse_attn(const int8_t* q8, const int8_t* k8, const uint16
   return out_dtype == PARO_F16 ? launch_attn<64, __half>(q8, k8, v16, p, s)
                                : launch_attn<64, __nv_bfloat16>(q8, k8, v16, p, s);
 }
+
+#ifdef PARO_ATTN_TRACE
+extern "C" int paro_debug_trace(unsigned long long* host16, int reset) {
+  if (host16) cudaMemcpyFromSymbol(host16, paro::g_trace, sizeof(unsigned long long) * 16);
+  if (reset) {
+    unsigned long long z[16] = {0};
+    cudaMemcpyToSymbol(paro::g_trace, z, sizeof(z));
+  }
+  return 0;
+}
+#endif
 
 extern "C" int paro_status_poll(const int32_t* status, int32_t* host_out, paro_stream_t stream) {
   PARO_REQUIRE(status, PARO_EINVAL, "paro_status_poll: null pointer");
