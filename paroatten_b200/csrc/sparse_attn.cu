@@ -4,14 +4,17 @@
 // tile -- the native tcgen05.mma M -- walking the union of the two blocks' kept k-blocks.  Each list
 // entry says which of the two halves keeps the block; the half that does not is given P = 0.
 //
-//   warps 0-3  one thread per q row: online softmax in fp32 (base 2, lazy rescaling), P written
-//              back over S in TMEM as fp16, epilogue O/l * v_scale + vm stored to the row's
-//              un-permuted position.  This warpgroup takes the registers the others give up.
-//   warp 4     TMA producer for Q (once) and the K ring (int8 tiles, freed as soon as Q.K^T is done)
-//   warp 5     TMA producer for the V^T ring (fp16 tiles, freed when P.V is done)
-//   warp 6     owns TMEM; one lane issues S = Q.K^T (kind::i8, int32 accumulators in TMEM) and
-//              O += P.V (kind::f16, P read from TMEM, fp32 accumulators in TMEM)
-//   warp 7     idle (completes the second warpgroup)
+//   warps 0-7   softmax + epilogue.  Row r of the tile is shared by two threads: warp w (< 4)
+//               takes score columns 0-31, warp w+4 columns 32-63 (both may touch TMEM lane
+//               quadrant w).  Online softmax in fp32 (base 2, lazy rescaling); the two threads
+//               exchange their partial row maximum through shared memory.  P is written back over S
+//               in TMEM as fp16; the epilogue stores O/l * v_scale + vm at the row's un-permuted
+//               position.  These warps take the registers the others give up.
+//   warp 8      TMA producer for Q (once) and the K ring (int8 tiles, freed when Q.K^T is done)
+//   warp 9      TMA producer for the V^T ring (fp16 tiles, freed when P.V is done)
+//   warp 10     owns TMEM; one lane issues S = Q.K^T (kind::i8, int32 accumulators in TMEM) and
+//               O += P.V (kind::f16, P read from TMEM, fp32 accumulators in TMEM)
+//   warp 11     idle (completes the third warpgroup)
 //
 // S is double buffered so that QK^T of tile i+1 overlaps the softmax of tile i; two CTAs share an
 // SM so that one CTA's softmax overlaps the other's MMAs.  Every wait is bounded: on expiry the
@@ -28,24 +31,21 @@ namespace paro {
 
 using namespace umma;
 
-constexpr int ATT_THREADS = 256;
+constexpr int ATT_THREADS = 384;
+constexpr int ATT_SOFTMAX_THREADS = 256;
 constexpr int TMEM_COLS = 256;              // S0 [0,64) S1 [64,128) O [128,128+D)
 constexpr long long WAIT_LIMIT = 400000000; // SM cycles (~0.2 s) before a wait gives up
 constexpr float RESCALE_TAU = 8.0f;         // rescale O only when the row max grows by > 2^8
 
 template <int D> struct AttnCfg {
   // ring depths, sized so that exactly two CTAs fit an SM (TMEM allows no more)
-#ifndef PARO_ATT_KST128
-#define PARO_ATT_KST128 5
-#define PARO_ATT_VST128 3
-#endif
-  static constexpr int K_STAGES = (D == 128) ? PARO_ATT_KST128 : 8;
-  static constexpr int V_STAGES = (D == 128) ? PARO_ATT_VST128 : 6;
+  static constexpr int K_STAGES = (D == 128) ? 4 : 8;
+  static constexpr int V_STAGES = (D == 128) ? 3 : 6;
   static constexpr int Q_BYTES = 128 * D;
   static constexpr int K_BYTES = 64 * D;
   static constexpr int V_BYTES = D * 128;   // D rows of 64 fp16
   static constexpr int TILE_BYTES = Q_BYTES + K_STAGES * K_BYTES + V_STAGES * V_BYTES;
-  static constexpr int AUX_BYTES = 2048;    // barriers, TMEM pointer, abort flag, v_scale, vm
+  static constexpr int AUX_BYTES = 4096;    // barriers, TMEM pointer, abort flag, v_scale, vm, row exchange
   static constexpr int SMEM_BYTES = TILE_BYTES + AUX_BYTES + 1024 /* alignment slack */;
 };
 
@@ -96,6 +96,9 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
   return r;
 }
+__device__ __forceinline__ void named_barrier(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
 
 __device__ __forceinline__ void report_timeout(const AttnParams& p, volatile int* abort_flag, int where, int iter) {
   if (atomicCAS(p.status, 0, PARO_ETIMEOUT) == 0) {
@@ -105,18 +108,6 @@ __device__ __forceinline__ void report_timeout(const AttnParams& p, volatile int
   }
   *abort_flag = 1;
 }
-
-// Optional cycle accounting of the roles (diagnostic builds only: -DPARO_ATTN_TRACE).
-#ifdef PARO_ATTN_TRACE
-__device__ unsigned long long g_trace[16];
-#define TRACE_DECL(cond) const bool tr_on = (cond); long long tr_t = clock64()
-#define TRACE_LAP(slot) do { if (tr_on) { const long long now__ = clock64(); atomicAdd(&g_trace[slot], (unsigned long long)(now__ - tr_t)); tr_t = now__; } } while (0)
-#define TRACE_COUNT(slot, n) do { if (tr_on) atomicAdd(&g_trace[slot], (unsigned long long)(n)); } while (0)
-#else
-#define TRACE_DECL(cond) do { } while (0)
-#define TRACE_LAP(slot) do { } while (0)
-#define TRACE_COUNT(slot, n) do { } while (0)
-#endif
 
 #define ATT_WAIT(bar, parity, where, iter)                                   \
   if (!mbar_wait_bounded((bar), (parity), abort_flag, WAIT_LIMIT)) {         \
@@ -148,9 +139,10 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   uint64_t* bar_pvdone = bar_pready + 2;                // [1]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_pvdone + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  float* s_vscale = reinterpret_cast<float*>(aux + 512);
-  float* s_vm = s_vscale + D;
-  static_assert(512 + 2 * D * 4 <= Cfg::AUX_BYTES, "aux area too small");
+  float* s_vscale = reinterpret_cast<float*>(aux + 512);   // [D]
+  float* s_vm = s_vscale + D;                              // [D]
+  float* s_xchg = reinterpret_cast<float*>(aux + 1536);    // [2 buffers][2 column halves][128 rows]
+  static_assert(512 + 2 * D * 4 <= 1536 && 1536 + 2 * 2 * 128 * 4 <= Cfg::AUX_BYTES, "aux area too small");
   static_assert((6 + 2 * KST + 2 * VST) * 8 + 8 <= 512, "barrier area too small");
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -172,13 +164,13 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar_sfull + i, 1);
-      mbar_init(bar_pready + i, 128);
+      mbar_init(bar_pready + i, ATT_SOFTMAX_THREADS / 32);
     }
     mbar_init(bar_pvdone, 1);
     *abort_flag = 0;
     fence_barrier_init();
   }
-  if (warp == 6) {
+  if (warp == 10) {
     tmem_alloc(tmem_slot, TMEM_COLS);
     tmem_relinquish();
   }
@@ -189,31 +181,26 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   const uint32_t tS[2] = {tmem_base, tmem_base + 64u};
   const uint32_t tO = tmem_base + 128u;
 
-  if (warp >= 4) asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
-  if (warp == 4) {
-    // ------------------------------------------------------------------ TMA producer: Q, K ring
-    if (lane == 0) {
+  if (warp >= 8) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 48;");
+    if (warp == 8 && lane == 0) {
+      // ---------------------------------------------------------------- TMA producer: Q, K ring
       tma_prefetch_desc(&tm_q);
       tma_prefetch_desc(&tm_k);
       mbar_arrive_expect_tx(bar_q, Cfg::Q_BYTES);
       tma_load_3d(sQ, &tm_q, 0, pair * 128, bh, bar_q);
-      TRACE_DECL(true);
       for (int i = 0; i < n_ent; ++i) {
         const int st = i % KST, use = i / KST;
         const int kb = ent[i] >> 2;
-        TRACE_LAP(15);
         if (use > 0) { ATT_WAIT(bar_kempty + st, (use - 1) & 1, 1, i) }
-        TRACE_LAP(14);
 #ifdef PARO_ABL_NO_TMA
         if (use > 0) { mbar_arrive(bar_kfull + st); continue; }
 #endif
         mbar_arrive_expect_tx(bar_kfull + st, Cfg::K_BYTES);
         tma_load_3d(sK + st * Cfg::K_BYTES, &tm_k, 0, kb * 64, bh, bar_kfull + st);
       }
-    }
-  } else if (warp == 5) {
-    // ------------------------------------------------------------------ TMA producer: V ring
-    if (lane == 0) {
+    } else if (warp == 9 && lane == 0) {
+      // ---------------------------------------------------------------- TMA producer: V ring
       tma_prefetch_desc(&tm_v);
       for (int i = 0; i < n_ent; ++i) {
         const int st = i % VST, use = i / VST;
@@ -225,10 +212,8 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         mbar_arrive_expect_tx(bar_vfull + st, Cfg::V_BYTES);
         tma_load_3d(sV + st * Cfg::V_BYTES, &tm_v, kb * 64, 0, bh, bar_vfull + st);
       }
-    }
-  } else if (warp == 6) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    } else if (warp == 10 && lane == 0) {
+      // ---------------------------------------------------------------- MMA issuer
       constexpr uint32_t IDESC_QK = instr_desc(2, 1, 1, 128, 64);  // s32 += s8 * s8
       constexpr uint32_t IDESC_PV = instr_desc(1, 0, 0, 128, D);   // f32 += f16 * f16
       const uint64_t dQ = smem_desc(smem_u32(sQ), D);
@@ -246,21 +231,17 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         ATT_WAIT(bar_kfull + 0, 0, 3, 0)
         tc_fence_after();
         issue_qk(0);
-        TRACE_DECL(true);
         for (int i = 0; i < n_ent; ++i) {
           const int st = i % VST;
-          TRACE_LAP(10);
           if (i + 1 < n_ent) {
             ATT_WAIT(bar_kfull + (i + 1) % KST, ((i + 1) / KST) & 1, 3, i + 1)
-            TRACE_LAP(11);
             tc_fence_after();
             issue_qk(i + 1);
           }
-          TRACE_LAP(10);
+#ifndef PARO_ABL_NO_PWAIT
           ATT_WAIT(bar_pready + (i & 1), (i >> 1) & 1, 4, i)
-          TRACE_LAP(12);
+#endif
           ATT_WAIT(bar_vfull + st, (i / VST) & 1, 5, i)
-          TRACE_LAP(13);
           tc_fence_after();
           const uint64_t dV = smem_desc(smem_u32(sV + st * Cfg::V_BYTES), 128);
 #pragma unroll
@@ -271,30 +252,39 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         }
       } while (false);
     }
-  } else if (warp < 4) {
+  } else {
     // ------------------------------------------------------------------ softmax + epilogue
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 200;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 96;");
     const int qd = warp & 3;                 // TMEM lane quadrant this warp may touch
+    const int ch = warp >> 2;                // which 32 score columns (and which half of O's columns)
     const int r = qd * 32 + lane;            // row inside the 128-row tile
     const int half = qd >> 1;                // which q-block of the pair
     const uint32_t lane_off = (uint32_t)(qd * 32) << 16;
-    const int tid = threadIdx.x;
-    if (tid < D) {
-      s_vscale[tid] = p.v_scale[(size_t)bh * D + tid];
-      s_vm[tid] = p.vm ? p.vm[(size_t)bh * D + tid] : 0.f;
+    if (threadIdx.x < D) {
+      s_vscale[threadIdx.x] = p.v_scale[(size_t)bh * D + threadIdx.x];
+      s_vm[threadIdx.x] = p.vm ? p.vm[(size_t)bh * D + threadIdx.x] : 0.f;
     }
-    asm volatile("bar.sync 1, 128;" ::: "memory");
+    named_barrier(1, ATT_SOFTMAX_THREADS);
 
     const int tok = pair * 128 + r;
     const int per_bh = p.nb * (64 / p.q_group);
     const float rowscale = (tok < p.N ? p.q_scale[(size_t)bh * per_bh + tok / p.q_group] : 0.f) * p.scale_log2;
-    float m = -INFINITY, l = 0.f;
+    float m = -INFINITY, l = 0.f;   // l: this thread's share of the row sum
     bool ok = true;
-    TRACE_DECL(warp == 0 && lane == 0);
-    TRACE_COUNT(9, n_ent);
+    // A parity wait can only tell "the phase before the current one is over", so every thread
+    // consumes every completion of the P.V barrier in order, one per tile: that of tile i-1 during
+    // tile i -- early if O has to be rescaled, otherwise after the exponentials, when it has long
+    // completed and costs nothing -- and the last one in the epilogue.
+    auto consume_pv = [&](int i) {
+      const bool good = __all_sync(0xffffffffu, mbar_wait_bounded(bar_pvdone, (i - 1) & 1, abort_flag, WAIT_LIMIT));
+      if (!good) report_timeout(p, abort_flag, 7, i);
+      tc_fence_after();
+      return good;
+    };
     const float* kscale_bh = p.k_scale + (size_t)bh * p.nb;
     int e_next = n_ent > 0 ? ent[0] : 0;
     float ks_next = n_ent > 0 ? kscale_bh[e_next >> 2] : 0.f;
+    int n_kept = 0;                 // kept tiles seen by this row: selects the exchange buffer
     for (int i = 0; i < n_ent; ++i) {
       const int e = e_next;
       const float kscale = ks_next;
@@ -304,60 +294,61 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         e_next = ent[i + 1];
         ks_next = kscale_bh[e_next >> 2];
       }
-      TRACE_LAP(0);
       ok = __all_sync(0xffffffffu, mbar_wait_bounded(bar_sfull + (i & 1), (i >> 1) & 1, abort_flag, WAIT_LIMIT));
       if (!ok) {
         report_timeout(p, abort_flag, 6, i);
         break;
       }
-      TRACE_LAP(1);
-      // A parity wait can only tell "the phase before the current one is over", so every thread
-      // consumes every completion of the P.V barrier in order: P.V of tile i-1 here (it was issued
-      // before this tile's scores were ready, so this costs nothing), the last one in the epilogue.
-      if (i > 0) {
-        ok = __all_sync(0xffffffffu, mbar_wait_bounded(bar_pvdone, (i - 1) & 1, abort_flag, WAIT_LIMIT));
-        if (!ok) {
-          report_timeout(p, abort_flag, 7, i);
-          break;
-        }
-      }
       tc_fence_after();
-      TRACE_LAP(2);
-      uint32_t pk[32];
+      uint32_t pk[16];
+      bool pv_consumed = (i == 0);
 #ifdef PARO_ABL_NO_EXP
       if (false) {
 #else
       if (keep) {
 #endif
-        TRACE_COUNT(8, 1);
-        uint32_t s[64];
-        tmem_ld32(tS[i & 1] + lane_off, s);
-        tmem_ld32(tS[i & 1] + lane_off + 32, s + 32);
-        tmem_wait_ld();
-        TRACE_LAP(3);
-        const int valid = min(64, p.N - kb * 64);
-        const float sc = rowscale * kscale;
-        // int32 scores -> fp32 (exact: |s| < 2^24); columns past the end of the sequence become -inf
-        float f[64];
+        float f[32];
+        {
+          uint32_t s[32];
+#ifdef PARO_ABL_NO_LD
 #pragma unroll
-        for (int j = 0; j < 64; ++j) f[j] = (float)(int)s[j];
-        if (valid < 64) {
+          for (int j = 0; j < 32; ++j) s[j] = (uint32_t)(j * lane + i);
+#else
+          tmem_ld32(tS[i & 1] + lane_off + 32 * ch, s);
+          tmem_wait_ld();
+#endif
+          // int32 scores -> fp32 (exact: |s| < 2^24)
 #pragma unroll
-          for (int j = 0; j < 64; ++j)
+          for (int j = 0; j < 32; ++j) f[j] = (float)(int)s[j];
+        }
+        const int valid = min(64, p.N - kb * 64) - 32 * ch;   // columns of mine inside the sequence
+        if (valid < 32) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
             if (j >= valid) f[j] = -INFINITY;
         }
         float mx4[4] = {f[0], f[1], f[2], f[3]};   // four independent chains of 3-input max
 #pragma unroll
-        for (int j = 4; j < 64; j += 8) {
+        for (int j = 4; j < 32; j += 8) {
           mx4[0] = max3(mx4[0], f[j], f[j + 1]);
           mx4[1] = max3(mx4[1], f[j + 2], f[j + 3]);
-          if (j + 4 < 64) {
+          if (j + 4 < 32) {
             mx4[2] = max3(mx4[2], f[j + 4], f[j + 5]);
             mx4[3] = max3(mx4[3], f[j + 6], f[j + 7]);
           }
         }
-        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sc;
-        TRACE_LAP(4);
+        const float my_max = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+        // the row's other 32 columns belong to the thread of warp (w ^ 4) with the same lane
+        float* xb = s_xchg + (n_kept & 1) * 256;
+        const float sc = rowscale * kscale;
+#ifdef PARO_ABL_NO_XCHG
+        const float mx = my_max * sc + xb[0];
+#else
+        xb[ch * 128 + r] = my_max;
+        named_barrier(2 + qd, 64);
+        const float mx = fmaxf(my_max, xb[(ch ^ 1) * 128 + r]) * sc;
+#endif
+        ++n_kept;
         float alpha = 1.f;
         bool resc = false;
         if (mx > m + RESCALE_TAU) {
@@ -366,44 +357,57 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           m = mx;
           l *= alpha;
         }
-        if (__any_sync(0xffffffffu, resc)) {  // the previous P.V has landed (waited above): O may be touched
+        if (__any_sync(0xffffffffu, resc)) {  // O may only be touched once the previous P.V has landed
+          if (!pv_consumed) {
+            pv_consumed = true;
+            ok = consume_pv(i);
+            if (!ok) break;
+          }
 #pragma unroll
-          for (int c = 0; c < D / 32; ++c) {
-            uint32_t o[32];
-            tmem_ld32(tO + lane_off + 32 * c, o);
+          for (int c = 0; c < D / 32; ++c) {  // this thread owns half of the row's O columns
+            uint32_t o[16];
+            const uint32_t addr = tO + lane_off + (uint32_t)(ch * (D / 2) + 16 * c);
+            tmem_ld16(addr, o);
             tmem_wait_ld();
 #pragma unroll
-            for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
-            tmem_st32(tO + lane_off + 32 * c, o);
+            for (int j = 0; j < 16; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
+            tmem_st16(addr, o);
           }
           tmem_wait_st();
         }
-        TRACE_LAP(5);
         const uint64_t sc2 = pack2(sc, sc), negm2 = pack2(-m, -m);
         uint64_t sum2[2] = {0ull, 0ull};
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
+        for (int j = 0; j < 16; ++j) {
           float x0, x1;
           unpack2(fma2(pack2(f[2 * j], f[2 * j + 1]), sc2, negm2), x0, x1);
+#ifdef PARO_ABL_NO_MUFU
+          const float p0 = x0, p1 = x1;
+#else
           const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);   // 2^-inf = 0 for masked columns
+#endif
           sum2[j & 1] = add2(sum2[j & 1], pack2(p0, p1));
           const __half2 h2 = __floats2half2_rn(p0, p1);
           pk[j] = *reinterpret_cast<const uint32_t*>(&h2);
         }
         float sa, sb;
         unpack2(add2(sum2[0], sum2[1]), sa, sb);
-        const float sum = sa + sb;
-        l += sum;
-        TRACE_LAP(6);
+        l += sa + sb;
       } else {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) pk[j] = 0u;
+        for (int j = 0; j < 16; ++j) pk[j] = 0u;
       }
-      tmem_st32(tS[i & 1] + lane_off, pk);
+      if (!pv_consumed) {
+        ok = consume_pv(i);
+        if (!ok) break;
+      }
+#ifndef PARO_ABL_NO_ST
+      tmem_st16(tS[i & 1] + lane_off + 16 * ch, pk);   // fp16 P: two values per 32-bit column
       tmem_wait_st();
+#endif
       tc_fence_before();
-      mbar_arrive(bar_pready + (i & 1));
-      TRACE_LAP(7);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_pready + (i & 1));   // one arrival per warp
     }
 
     // epilogue (the TMEM loads are warp-collective: every lane of the warp executes them, rows past
@@ -413,19 +417,25 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       if (!ok) report_timeout(p, abort_flag, 8, n_ent);
       tc_fence_after();
     }
+    // row sum = both threads' shares (reached by every softmax thread, also after a failed wait)
+    float* xl = s_xchg + 512 - 256;   // second buffer is free again only after the loop: use a barrier first
+    named_barrier(1, ATT_SOFTMAX_THREADS);
+    xl[ch * 128 + r] = l;
+    named_barrier(1, ATT_SOFTMAX_THREADS);
+    l += xl[(ch ^ 1) * 128 + r];
     if (ok) {
       const int b = bh / p.H, h = bh % p.H;
       const bool live = tok < p.N;
       int dst = tok;
       if (live && p.inv_idx && tok >= p.n_text)
         dst = p.n_text + p.inv_idx[(size_t)h * (p.N - p.n_text) + (tok - p.n_text)];
-      OutT* orow = static_cast<OutT*>(p.out) + b * p.osb + h * p.osh + (int64_t)dst * p.osn;
+      OutT* orow = static_cast<OutT*>(p.out) + b * p.osb + h * p.osh + (int64_t)dst * p.osn + ch * (D / 2);
       const float inv_l = l > 0.f ? 1.f / l : 0.f;
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = 0; c < D / 64; ++c) {
         uint32_t o[32];
         if (n_ent > 0) {
-          tmem_ld32(tO + lane_off + 32 * c, o);
+          tmem_ld32(tO + lane_off + (uint32_t)(ch * (D / 2) + 32 * c), o);
           tmem_wait_ld();
         } else {
 #pragma unroll
@@ -434,7 +444,7 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         uint32_t w[16];
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
-          const int d0 = 32 * c + 2 * j;
+          const int d0 = ch * (D / 2) + 32 * c + 2 * j;
           const float a0 = l > 0.f ? fmaf(__uint_as_float(o[2 * j]) * inv_l, s_vscale[d0], s_vm[d0]) : 0.f;
           const float a1 = l > 0.f ? fmaf(__uint_as_float(o[2 * j + 1]) * inv_l, s_vscale[d0 + 1], s_vm[d0 + 1]) : 0.f;
           OutT t[2] = {F16Traits<OutT>::from_float(a0), F16Traits<OutT>::from_float(a1)};
@@ -446,13 +456,14 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             *reinterpret_cast<uint4*>(orow + 32 * c + 8 * j) = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
         }
       }
-      if (live && p.lse) p.lse[(size_t)bh * p.N + dst] = l > 0.f ? (log2f(l) + m) * 0.6931471805599453f : -INFINITY;
+      if (live && ch == 0 && p.lse)
+        p.lse[(size_t)bh * p.N + dst] = l > 0.f ? (log2f(l) + m) * 0.6931471805599453f : -INFINITY;
     }
   }
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 6) {
+  if (warp == 10) {
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
