@@ -78,6 +78,23 @@ int paro_channel_mean(const void* x, int dtype, int B, int H, int N, int D,
                       void* mean_out, float* mean_f32, void* scratch, size_t scratch_bytes,
                       paro_stream_t stream);
 
+/* paro_channel_mean for callers that cannot allocate device memory -- for example a server whose
+ * memory pool is frozen after warm-up, a C host with no allocator to take scratch from, or a
+ * latency-critical loop where a cudaMalloc would stall the device.  No counterpart in the
+ * reference.  Same inputs, outputs and results as paro_channel_mean; the partial sums live in a
+ * 16 MiB array built into the library (held on every GPU that loads it, until the process exits)
+ * instead of caller scratch.  Limits and rules:
+ *   - B*H*ceil(N/512)*D*16 bytes must fit in 16 MiB, otherwise PARO_ECAP (nothing is launched);
+ *   - the call allocates nothing (no cudaMalloc/cudaFree, no allocating library routine);
+ *   - the first call on each device looks up the array's device address (cudaGetSymbolAddress),
+ *     so make that first call before starting any stream capture;
+ *   - all calls on a device share the one array: calls that may overlap on the GPU (different
+ *     streams without ordering) race and must be serialised by the caller.  The array keeps the
+ *     previous call's contents; every value a call reads is written by that call first. */
+int paro_channel_mean_noalloc(const void* x, int dtype, int B, int H, int N, int D,
+                              int64_t stride_b, int64_t stride_h, int64_t stride_n,
+                              void* mean_out, float* mean_f32, paro_stream_t stream);
+
 /* Per-group symmetric INT8: group = 32 (the reference's per-warp Q, quant.py:105-180 ->
  * fused.cu:685-768) or 64 (per-block Q/K, fused.cu:429-682).  km (nullable, [B,H,D], input
  * dtype) is subtracted first (fused.cu:594-682); fold_scale != 0 multiplies x before

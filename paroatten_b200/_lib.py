@@ -69,6 +69,7 @@ SIGNATURES = {
                                  _vp, _i32, _i32, _vp, _vp, _i32, _i32, _vp]),
     "paro_channel_stats_scratch_bytes": (_sz, [_i32, _i32, _i32, _i32]),
     "paro_channel_mean": (_i32, [_vp, _i32, _i32, _i32, _i32, _i32, _i64, _i64, _i64, _vp, _vp, _vp, _sz, _vp]),
+    "paro_channel_mean_noalloc": (_i32, [_vp, _i32, _i32, _i32, _i32, _i32, _i64, _i64, _i64, _vp, _vp, _vp]),
     "paro_quant_int8": (_i32, [_vp, _i32, _i32, _i32, _i32, _i32, _i64, _i64, _i64, _vp, _f32, _i32, _vp, _vp, _vp]),
     "paro_quant_v_fp8": (_i32, [_vp, _i32, _i32, _i32, _i32, _i32, _i64, _i64, _i64, _i32, _f32, _vp, _vp, _vp, _vp,
                                 _vp, _sz, _vp]),

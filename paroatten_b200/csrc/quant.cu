@@ -3,6 +3,8 @@
 // pass, results compared bit-for-bit with the CPU oracle (IEEE divide/multiply, no fast-math).
 #include <cuda_fp8.h>
 
+#include <mutex>
+
 #include "common.cuh"
 
 namespace paro {
@@ -363,4 +365,71 @@ extern "C" int paro_quant_v_fp8(const void* v, int dtype, int B, int H, int N, i
   return dtype == PARO_F16
              ? run_v_fp8<__half>(v, B, H, N, D, stride_b, stride_h, stride_n, smooth, scale_max, v8, v16, v_scale, vm, scratch, s)
              : run_v_fp8<__nv_bfloat16>(v, B, H, N, D, stride_b, stride_h, stride_n, smooth, scale_max, v8, v16, v_scale, vm, scratch, s);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Channel mean for callers that must not allocate.
+//
+// Some users of this library run where asking for device memory is off the table: an inference
+// server that froze its memory pool after warm-up, a plain C host that has no allocator of its own
+// to draw a scratch buffer from, or a latency-critical denoising loop in which a cudaMalloc would
+// stall the whole device.  For them the reduction's partial sums live in the fixed array below
+// instead of a caller-provided buffer.  The array is part of the loaded module, so every GPU that
+// loads the library sets aside its 16 MiB until the process exits.
+namespace {
+
+constexpr size_t NOALLOC_SCRATCH_BYTES = 16u << 20;   // 16 MiB: enough for B*H*ceil(N/512)*D <= 1,040,000
+static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_SCRATCH_BYTES];
+
+constexpr int NOALLOC_MAX_DEVICES = 64;
+std::mutex g_noalloc_mutex;
+void* g_noalloc_ptr[NOALLOC_MAX_DEVICES] = {};
+
+// Device address of g_noalloc_scratch on the CURRENT device.  In host code the array's name is
+// only a handle for the runtime, never a pointer a kernel may use, so the address is looked up
+// once per device (with that device current) and remembered.
+int noalloc_scratch(void** out) {
+  int dev = -1;
+  PARO_CUDA_OK(cudaGetDevice(&dev));
+  PARO_REQUIRE(dev >= 0 && dev < NOALLOC_MAX_DEVICES, PARO_ECUDA, "device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  if (g_noalloc_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    PARO_CUDA_OK(cudaGetSymbolAddress(&p, g_noalloc_scratch));
+    PARO_REQUIRE(p != nullptr, PARO_ECUDA, "cudaGetSymbolAddress returned a null address");
+    g_noalloc_ptr[dev] = p;
+  }
+  *out = g_noalloc_ptr[dev];
+  return PARO_OK;
+}
+
+}  // namespace
+
+extern "C" int paro_channel_mean_noalloc(const void* x, int dtype, int B, int H, int N, int D,
+                                         int64_t stride_b, int64_t stride_h, int64_t stride_n,
+                                         void* mean_out, float* mean_f32, paro_stream_t stream) {
+  if (int rc = check_tensor("paro_channel_mean_noalloc(x)", x, dtype, B, H, N, D, stride_b, stride_h, stride_n)) return rc;
+  PARO_REQUIRE(mean_out || mean_f32, PARO_EINVAL, "paro_channel_mean_noalloc: no output requested");
+  const unsigned long long need =
+      (unsigned long long)B * H * (unsigned long long)stats_chunks(N) * D * sizeof(ChannelPartial);
+  PARO_REQUIRE(need <= NOALLOC_SCRATCH_BYTES, PARO_ECAP,
+               "paro_channel_mean_noalloc: this problem needs %llu bytes of scratch but the built-in scratch holds "
+               "%zu; use paro_channel_mean with a caller-provided buffer", need, (size_t)NOALLOC_SCRATCH_BYTES);
+  void* scratch = nullptr;
+  if (int rc = noalloc_scratch(&scratch)) return rc;
+  cudaStream_t s = (cudaStream_t)stream;
+  ChannelPartial* part = static_cast<ChannelPartial*>(scratch);
+  // every partial the second pass reads is written by the first pass of the same call, so nothing
+  // left behind by an earlier call has to be cleared
+  if (dtype == PARO_F16) {
+    launch_stats<__half>(x, B, H, N, D, stride_b, stride_h, stride_n, part, s);
+    channel_finalize_kernel<__half><<<B * H, D, 0, s>>>(part, stats_chunks(N), D, N, 1, 1.f, (__half*)mean_out,
+                                                        mean_f32, nullptr, nullptr, nullptr);
+  } else {
+    launch_stats<__nv_bfloat16>(x, B, H, N, D, stride_b, stride_h, stride_n, part, s);
+    channel_finalize_kernel<__nv_bfloat16><<<B * H, D, 0, s>>>(part, stats_chunks(N), D, N, 1, 1.f,
+                                                               (__nv_bfloat16*)mean_out, mean_f32, nullptr, nullptr,
+                                                               nullptr);
+  }
+  return check_launch("channel_mean_noalloc", 2);
 }
