@@ -31,28 +31,46 @@ def _nvcc():
     return cand if os.path.exists(cand) else None
 
 
+HASH_PATH = LIB_PATH + ".srchash"
+
+
+def _source_hash() -> str:
+    """Digest of everything the library is built from (file times do not survive copying a tree)."""
+    import hashlib
+    h = hashlib.sha256(" ".join(NVCC_FLAGS).encode())
+    files = sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC)) + [os.path.join(HERE, "..", "include", "paro_b200.h")]
+    for f in files:
+        with open(f, "rb") as fh:
+            h.update(os.path.basename(f).encode() + b"\0" + fh.read())
+    return h.hexdigest()
+
+
 def _stale() -> bool:
-    if not os.path.exists(LIB_PATH):
+    if not (os.path.exists(LIB_PATH) and os.path.exists(HASH_PATH)):
         return True
-    t = os.path.getmtime(LIB_PATH)
-    deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)] + [os.path.join(HERE, "..", "include", "paro_b200.h")]
-    return any(os.path.exists(d) and os.path.getmtime(d) > t for d in deps)
+    with open(HASH_PATH) as fh:
+        return fh.read().strip() != _source_hash()
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
-    """Compiles csrc/*.cu for sm_100a into libparo_b200.so next to this file."""
+    """Compiles csrc/*.cu for sm_100a into libparo_b200.so next to this file.  Safe against
+    several processes building at once (each writes its own temporary file, renames are atomic)."""
     with _lock:
         if not force and not _stale():
             return LIB_PATH
         nvcc = _nvcc()
         if nvcc is None:
             raise RuntimeError("libparo_b200.so is missing or out of date and nvcc was not found to build it")
+        tmp = f"{LIB_PATH}.{os.getpid()}.tmp"
         cmd = [nvcc, *NVCC_FLAGS, *(["-Xptxas", "-v"] if verbose else []),
-               *[os.path.join(CSRC, s) for s in SOURCES], "-o", LIB_PATH + ".tmp"]
+               *[os.path.join(CSRC, s) for s in SOURCES], "-o", tmp]
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode != 0:
             raise RuntimeError("nvcc failed:\n" + res.stdout + res.stderr)
-        os.replace(LIB_PATH + ".tmp", LIB_PATH)
+        os.replace(tmp, LIB_PATH)
+        with open(f"{HASH_PATH}.{os.getpid()}.tmp", "w") as fh:
+            fh.write(_source_hash())
+        os.replace(f"{HASH_PATH}.{os.getpid()}.tmp", HASH_PATH)
         if verbose:
             print(res.stderr)
         return LIB_PATH
