@@ -130,20 +130,20 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   uint8_t* sV = sK + KST * Cfg::K_BYTES;
   uint8_t* aux = smem + Cfg::TILE_BYTES;
   uint64_t* bar_q = reinterpret_cast<uint64_t*>(aux);   // [1]
-  uint64_t* bar_kfull = bar_q + 1;                      // [KST]
-  uint64_t* bar_kempty = bar_kfull + KST;               // [KST]
-  uint64_t* bar_vfull = bar_kempty + KST;               // [VST]
-  uint64_t* bar_vempty = bar_vfull + VST;               // [VST]
-  uint64_t* bar_sfull = bar_vempty + VST;               // [2]
-  uint64_t* bar_pready = bar_sfull + 2;                 // [2]
-  uint64_t* bar_pvdone = bar_pready + 2;                // [1]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_pvdone + 1);
+  uint64_t* bar_kfull = bar_q + 1;                      // [KST]  K tile landed
+  uint64_t* bar_qkdone = bar_kfull + KST;               // [KST]  Q.K^T of the tile in this K stage finished:
+                                                        //        scores ready (softmax) and K stage free (producer)
+  uint64_t* bar_vfull = bar_qkdone + KST;               // [VST]  V tile landed
+  uint64_t* bar_pvdone = bar_vfull + VST;               // [VST]  P.V of the tile in this V stage finished:
+                                                        //        O up to date (softmax) and V stage free (producer)
+  uint64_t* bar_pready = bar_pvdone + VST;              // [2]    P written (softmax -> MMA issuer)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_pready + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* s_vscale = reinterpret_cast<float*>(aux + 512);   // [D]
   float* s_vm = s_vscale + D;                              // [D]
   float* s_xchg = reinterpret_cast<float*>(aux + 1536);    // [2 buffers][2 column halves][128 rows]
   static_assert(512 + 2 * D * 4 <= 1536 && 1536 + 2 * 2 * 128 * 4 <= Cfg::AUX_BYTES, "aux area too small");
-  static_assert((6 + 2 * KST + 2 * VST) * 8 + 8 <= 512, "barrier area too small");
+  static_assert((3 + 2 * KST + 2 * VST) * 8 + 8 <= 512, "barrier area too small");
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int bh = blockIdx.x / p.npairs, pair = blockIdx.x % p.npairs;
@@ -156,17 +156,13 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     mbar_init(bar_q, 1);
     for (int i = 0; i < KST; ++i) {
       mbar_init(bar_kfull + i, 1);
-      mbar_init(bar_kempty + i, 1);
+      mbar_init(bar_qkdone + i, 1);
     }
     for (int i = 0; i < VST; ++i) {
       mbar_init(bar_vfull + i, 1);
-      mbar_init(bar_vempty + i, 1);
+      mbar_init(bar_pvdone + i, 1);
     }
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(bar_sfull + i, 1);
-      mbar_init(bar_pready + i, ATT_SOFTMAX_THREADS / 32);
-    }
-    mbar_init(bar_pvdone, 1);
+    for (int i = 0; i < 2; ++i) mbar_init(bar_pready + i, ATT_SOFTMAX_THREADS / 32);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -192,7 +188,7 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       for (int i = 0; i < n_ent; ++i) {
         const int st = i % KST, use = i / KST;
         const int kb = ent[i] >> 2;
-        if (use > 0) { ATT_WAIT(bar_kempty + st, (use - 1) & 1, 1, i) }
+        if (use > 0) { ATT_WAIT(bar_qkdone + st, (use - 1) & 1, 1, i) }
 #ifdef PARO_ABL_NO_TMA
         if (use > 0) { mbar_arrive(bar_kfull + st); continue; }
 #endif
@@ -205,7 +201,7 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       for (int i = 0; i < n_ent; ++i) {
         const int st = i % VST, use = i / VST;
         const int kb = ent[i] >> 2;
-        if (use > 0) { ATT_WAIT(bar_vempty + st, (use - 1) & 1, 9, i) }
+        if (use > 0) { ATT_WAIT(bar_pvdone + st, (use - 1) & 1, 9, i) }
 #ifdef PARO_ABL_NO_TMA
         if (use > 0) { mbar_arrive(bar_vfull + st); continue; }
 #endif
@@ -222,8 +218,7 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 #pragma unroll
         for (int k = 0; k < D / 32; ++k)
           mma_i8_ss(tS[i & 1], desc_advance(dQ, 32 * k), desc_advance(dK, 32 * k), IDESC_QK, k > 0);
-        mma_commit(bar_sfull + (i & 1));
-        mma_commit(bar_kempty + i % KST);
+        mma_commit(bar_qkdone + i % KST);
       };
       do {
         ATT_WAIT(bar_q, 0, 2, -1)
@@ -247,8 +242,7 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 #pragma unroll
           for (int k = 0; k < 4; ++k)
             mma_f16_ts(tO, tS[i & 1] + 8 * k, desc_advance(dV, 32 * k), IDESC_PV, (i > 0 || k > 0) ? 1u : 0u);
-          mma_commit(bar_vempty + st);
-          mma_commit(bar_pvdone);
+          mma_commit(bar_pvdone + st);
         }
       } while (false);
     }
@@ -271,15 +265,16 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     const float rowscale = (tok < p.N ? p.q_scale[(size_t)bh * per_bh + tok / p.q_group] : 0.f) * p.scale_log2;
     float m = -INFINITY, l = 0.f;   // l: this thread's share of the row sum
     bool ok = true;
-    // A parity wait can only tell "the phase before the current one is over", so every thread
-    // consumes every completion of the P.V barrier in order, one per tile: that of tile i-1 during
-    // tile i -- early if O has to be rescaled, otherwise after the exponentials, when it has long
-    // completed and costs nothing -- and the last one in the epilogue.
-    auto consume_pv = [&](int i) {
+    // A parity wait can only tell "the phase before the current one is over", so every waiter
+    // consumes every completion of a barrier in order.  The softmax threads therefore wait for the
+    // P.V of tile i-1 during tile i -- early if O has to be rescaled, otherwise after the exponentials,
+    // when it has long completed and costs nothing -- and for the last one in the epilogue.
+    auto consume_pv = [&](int i) {   // P.V of tile i-1
 #ifdef PARO_ABL_FREE_RUN
       return true;
 #endif
-      const bool good = __all_sync(0xffffffffu, mbar_wait_bounded(bar_pvdone, (i - 1) & 1, abort_flag, WAIT_LIMIT));
+      const bool good = __all_sync(0xffffffffu, mbar_wait_bounded(bar_pvdone + (i - 1) % VST, ((i - 1) / VST) & 1,
+                                                                  abort_flag, WAIT_LIMIT));
       if (!good) report_timeout(p, abort_flag, 7, i);
       tc_fence_after();
       return good;
@@ -298,7 +293,7 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         ks_next = kscale_bh[e_next >> 2];
       }
 #ifndef PARO_ABL_FREE_RUN
-      ok = __all_sync(0xffffffffu, mbar_wait_bounded(bar_sfull + (i & 1), (i >> 1) & 1, abort_flag, WAIT_LIMIT));
+      ok = __all_sync(0xffffffffu, mbar_wait_bounded(bar_qkdone + i % KST, (i / KST) & 1, abort_flag, WAIT_LIMIT));
       if (!ok) {
         report_timeout(p, abort_flag, 6, i);
         break;
@@ -422,7 +417,8 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 #else
     if (ok && n_ent > 0) {
 #endif
-      ok = __all_sync(0xffffffffu, mbar_wait_bounded(bar_pvdone, (n_ent - 1) & 1, abort_flag, WAIT_LIMIT));
+      ok = __all_sync(0xffffffffu, mbar_wait_bounded(bar_pvdone + (n_ent - 1) % VST, ((n_ent - 1) / VST) & 1,
+                                                     abort_flag, WAIT_LIMIT));
       if (!ok) report_timeout(p, abort_flag, 8, n_ent);
       tc_fence_after();
     }
