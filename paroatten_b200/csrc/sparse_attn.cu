@@ -10,14 +10,17 @@
 //               exchange their partial row maximum through shared memory.  P is written back over S
 //               in TMEM as fp16; the epilogue stores O/l * v_scale + vm at the row's un-permuted
 //               position.  These warps take the registers the others give up.
-//   warp 8      TMA producer for Q (once) and the K ring (int8 tiles, freed when Q.K^T is done)
+//   warp 8      TMA producer for the K ring (int8 tiles, freed when Q.K^T is done)
 //   warp 9      TMA producer for the V^T ring (fp16 tiles, freed when P.V is done)
 //   warp 10     owns TMEM; one lane issues S = Q.K^T (kind::i8, int32 accumulators in TMEM) and
 //               O += P.V (kind::f16, P read from TMEM, fp32 accumulators in TMEM)
 //   warp 11     idle (completes the third warpgroup)
 //
-// S is double buffered so that QK^T of tile i+1 overlaps the softmax of tile i; two CTAs share an
-// SM so that one CTA's softmax overlaps the other's MMAs.  Every wait is bounded: on expiry the
+// TMEM (256 columns per CTA): S [0,64) int32 scores, P [64,96) fp16 probabilities, Q [96,128) the
+// int8 query tile (A operand of Q.K^T read from TMEM, so it is not re-read from shared memory for
+// every k-block), O [128,128+D) fp32.  The softmax threads release S as soon as they hold the scores
+// in registers, so Q.K^T of tile i+1 overlaps the exponentials of tile i, and P.V of tile i overlaps
+// the softmax of tile i+1; two CTAs share an SM so that one CTA's softmax overlaps the other's MMAs.  Every wait is bounded: on expiry the
 // CTA records a code in the status words, raises a shared abort flag and unwinds (TMEM freed).
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -33,23 +36,23 @@ using namespace umma;
 
 constexpr int ATT_THREADS = 384;
 constexpr int ATT_SOFTMAX_THREADS = 256;
-constexpr int TMEM_COLS = 256;              // S0 [0,64) S1 [64,128) O [128,128+D)
+constexpr int TMEM_COLS = 256;
 constexpr long long WAIT_LIMIT = 400000000; // SM cycles (~0.2 s) before a wait gives up
 constexpr float RESCALE_TAU = 8.0f;         // rescale O only when the row max grows by > 2^8
 
 template <int D> struct AttnCfg {
   // ring depths, sized so that exactly two CTAs fit an SM (TMEM allows no more)
-  static constexpr int K_STAGES = (D == 128) ? 4 : 8;
-  static constexpr int V_STAGES = (D == 128) ? 3 : 6;
-  static constexpr int Q_BYTES = 128 * D;
+  static constexpr int K_STAGES = (D == 128) ? 5 : 8;
+  static constexpr int V_STAGES = (D == 128) ? 4 : 7;
   static constexpr int K_BYTES = 64 * D;
   static constexpr int V_BYTES = D * 128;   // D rows of 64 fp16
-  static constexpr int TILE_BYTES = Q_BYTES + K_STAGES * K_BYTES + V_STAGES * V_BYTES;
+  static constexpr int TILE_BYTES = K_STAGES * K_BYTES + V_STAGES * V_BYTES;
   static constexpr int AUX_BYTES = 4096;    // barriers, TMEM pointer, abort flag, v_scale, vm, row exchange
   static constexpr int SMEM_BYTES = TILE_BYTES + AUX_BYTES + 1024 /* alignment slack */;
 };
 
 struct AttnParams {
+  const int8_t* q8;
   const float* q_scale;
   const float* k_scale;
   const float* v_scale;
@@ -117,27 +120,27 @@ __device__ __forceinline__ void report_timeout(const AttnParams& p, volatile int
 
 template <int D, typename OutT>
 __global__ void __launch_bounds__(ATT_THREADS, 2)
-sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                   const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
+sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                   const AttnParams p) {
   using Cfg = AttnCfg<D>;
   constexpr int KST = Cfg::K_STAGES, VST = Cfg::V_STAGES;
   if (*reinterpret_cast<volatile int32_t*>(p.status) != 0) return;  // an earlier CTA failed: drain quickly
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* sQ = smem;
-  uint8_t* sK = sQ + Cfg::Q_BYTES;
+  uint8_t* sK = smem;
   uint8_t* sV = sK + KST * Cfg::K_BYTES;
   uint8_t* aux = smem + Cfg::TILE_BYTES;
-  uint64_t* bar_q = reinterpret_cast<uint64_t*>(aux);   // [1]
+  uint64_t* bar_q = reinterpret_cast<uint64_t*>(aux);   // [1]    Q tile stored in TMEM (softmax -> MMA issuer)
   uint64_t* bar_kfull = bar_q + 1;                      // [KST]  K tile landed
   uint64_t* bar_qkdone = bar_kfull + KST;               // [KST]  Q.K^T of the tile in this K stage finished:
                                                         //        scores ready (softmax) and K stage free (producer)
   uint64_t* bar_vfull = bar_qkdone + KST;               // [VST]  V tile landed
   uint64_t* bar_pvdone = bar_vfull + VST;               // [VST]  P.V of the tile in this V stage finished:
                                                         //        O up to date (softmax) and V stage free (producer)
-  uint64_t* bar_pready = bar_pvdone + VST;              // [2]    P written (softmax -> MMA issuer)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_pready + 2);
+  uint64_t* bar_pready = bar_pvdone + VST;              // [1]    P written (softmax -> MMA issuer)
+  uint64_t* bar_sfree = bar_pready + 1;                 // [1]    scores copied to registers (softmax -> MMA issuer)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_sfree + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* s_vscale = reinterpret_cast<float*>(aux + 512);   // [D]
   float* s_vm = s_vscale + D;                              // [D]
@@ -153,7 +156,7 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   const int32_t* ent = p.pair_ent + ent0;
 
   if (threadIdx.x == 0) {
-    mbar_init(bar_q, 1);
+    mbar_init(bar_q, 4);
     for (int i = 0; i < KST; ++i) {
       mbar_init(bar_kfull + i, 1);
       mbar_init(bar_qkdone + i, 1);
@@ -162,7 +165,8 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       mbar_init(bar_vfull + i, 1);
       mbar_init(bar_pvdone + i, 1);
     }
-    for (int i = 0; i < 2; ++i) mbar_init(bar_pready + i, ATT_SOFTMAX_THREADS / 32);
+    mbar_init(bar_pready, ATT_SOFTMAX_THREADS / 32);
+    mbar_init(bar_sfree, ATT_SOFTMAX_THREADS / 32);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -174,17 +178,13 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tS[2] = {tmem_base, tmem_base + 64u};
-  const uint32_t tO = tmem_base + 128u;
+  const uint32_t tS = tmem_base, tP = tmem_base + 64u, tQ = tmem_base + 96u, tO = tmem_base + 128u;
 
   if (warp >= 8) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 48;");
     if (warp == 8 && lane == 0) {
       // ---------------------------------------------------------------- TMA producer: Q, K ring
-      tma_prefetch_desc(&tm_q);
       tma_prefetch_desc(&tm_k);
-      mbar_arrive_expect_tx(bar_q, Cfg::Q_BYTES);
-      tma_load_3d(sQ, &tm_q, 0, pair * 128, bh, bar_q);
       for (int i = 0; i < n_ent; ++i) {
         const int st = i % KST, use = i / KST;
         const int kb = ent[i] >> 2;
@@ -212,12 +212,11 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       // ---------------------------------------------------------------- MMA issuer
       constexpr uint32_t IDESC_QK = instr_desc(2, 1, 1, 128, 64);  // s32 += s8 * s8
       constexpr uint32_t IDESC_PV = instr_desc(1, 0, 0, 128, D);   // f32 += f16 * f16
-      const uint64_t dQ = smem_desc(smem_u32(sQ), D);
       auto issue_qk = [&](int i) {
         const uint64_t dK = smem_desc(smem_u32(sK + (i % KST) * Cfg::K_BYTES), D);
 #pragma unroll
         for (int k = 0; k < D / 32; ++k)
-          mma_i8_ss(tS[i & 1], desc_advance(dQ, 32 * k), desc_advance(dK, 32 * k), IDESC_QK, k > 0);
+          mma_i8_ts(tS, tQ + 8 * k, desc_advance(dK, 32 * k), IDESC_QK, k > 0);
         mma_commit(bar_qkdone + i % KST);
       };
       do {
@@ -230,18 +229,19 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           const int st = i % VST;
           if (i + 1 < n_ent) {
             ATT_WAIT(bar_kfull + (i + 1) % KST, ((i + 1) / KST) & 1, 3, i + 1)
+            ATT_WAIT(bar_sfree, i & 1, 10, i)     // the scores of tile i are in registers: S may be overwritten
             tc_fence_after();
             issue_qk(i + 1);
           }
 #ifndef PARO_ABL_NO_PWAIT
-          ATT_WAIT(bar_pready + (i & 1), (i >> 1) & 1, 4, i)
+          ATT_WAIT(bar_pready, i & 1, 4, i)
 #endif
           ATT_WAIT(bar_vfull + st, (i / VST) & 1, 5, i)
           tc_fence_after();
           const uint64_t dV = smem_desc(smem_u32(sV + st * Cfg::V_BYTES), 128);
 #pragma unroll
           for (int k = 0; k < 4; ++k)
-            mma_f16_ts(tO, tS[i & 1] + 8 * k, desc_advance(dV, 32 * k), IDESC_PV, (i > 0 || k > 0) ? 1u : 0u);
+            mma_f16_ts(tO, tP + 8 * k, desc_advance(dV, 32 * k), IDESC_PV, (i > 0 || k > 0) ? 1u : 0u);
           mma_commit(bar_pvdone + st);
         }
       } while (false);
@@ -261,6 +261,21 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     named_barrier(1, ATT_SOFTMAX_THREADS);
 
     const int tok = pair * 128 + r;
+    if (ch == 0) {
+      // this thread's query row goes to TMEM (four int8 per 32-bit column); rows past the end are zero
+      uint32_t qrow[D / 4];
+      const uint4* src = reinterpret_cast<const uint4*>(p.q8 + ((size_t)bh * p.N + (tok < p.N ? tok : 0)) * D);
+#pragma unroll
+      for (int j = 0; j < D / 16; ++j) {
+        const uint4 v4 = tok < p.N ? src[j] : make_uint4(0, 0, 0, 0);
+        qrow[4 * j] = v4.x; qrow[4 * j + 1] = v4.y; qrow[4 * j + 2] = v4.z; qrow[4 * j + 3] = v4.w;
+      }
+      if (D == 128) tmem_st32(tQ + lane_off, qrow); else tmem_st16(tQ + lane_off, qrow);
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_q);
+    }
     const int per_bh = p.nb * (64 / p.q_group);
     const float rowscale = (tok < p.N ? p.q_scale[(size_t)bh * per_bh + tok / p.q_group] : 0.f) * p.scale_log2;
     float m = -INFINITY, l = 0.f;   // l: this thread's share of the row sum
@@ -314,9 +329,13 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 #pragma unroll
           for (int j = 0; j < 32; ++j) s[j] = (uint32_t)(j * lane + i);
 #else
-          tmem_ld32(tS[i & 1] + lane_off + 32 * ch, s);
+          tmem_ld32(tS + lane_off + 32 * ch, s);
           tmem_wait_ld();
 #endif
+          // the scores are in registers: let the issuer overwrite S with the next tile's
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_sfree);
           // int32 scores -> fp32 (exact: |s| < 2^24)
 #pragma unroll
           for (int j = 0; j < 32; ++j) f[j] = (float)(int)s[j];
@@ -394,6 +413,8 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         unpack2(add2(sum2[0], sum2[1]), sa, sb);
         l += sa + sb;
       } else {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_sfree);
 #pragma unroll
         for (int j = 0; j < 16; ++j) pk[j] = 0u;
       }
@@ -402,12 +423,12 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         if (!ok) break;
       }
 #ifndef PARO_ABL_NO_ST
-      tmem_st16(tS[i & 1] + lane_off + 16 * ch, pk);   // fp16 P: two values per 32-bit column
+      tmem_st16(tP + lane_off + 16 * ch, pk);   // fp16 P: two values per 32-bit column
       tmem_wait_st();
 #endif
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar_pready + (i & 1));   // one arrival per warp
+      if (lane == 0) mbar_arrive(bar_pready);   // one arrival per warp
     }
 
     // epilogue (the TMEM loads are warp-collective: every lane of the warp executes them, rows past
@@ -513,8 +534,7 @@ static int launch_attn(const int8_t* q8, const int8_t* k8, const uint16_t* v16, 
   const uint64_t BH = (uint64_t)p.B * p.H;
   const uint64_t npad = (uint64_t)p.nb * 64;
   const CUtensorMapSwizzle swz_qk = D == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
-  CUtensorMap tq, tk, tv;
-  if (int rc = make_map(&tq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, q8, D, p.N, BH, D, 128, swz_qk)) return rc;
+  CUtensorMap tk, tv;
   if (int rc = make_map(&tk, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, k8, D, p.N, BH, D, 64, swz_qk)) return rc;
   if (int rc = make_map(&tv, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, v16, npad, D, BH, 64, D, CU_TENSOR_MAP_SWIZZLE_128B))
     return rc;
@@ -522,7 +542,7 @@ static int launch_attn(const int8_t* q8, const int8_t* k8, const uint16_t* v16, 
   PARO_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
   const uint64_t ctas = BH * p.npairs;
   PARO_REQUIRE(ctas < (1ull << 31), PARO_ESHAPE, "paro_sparse_attn: too many work items");
-  kern<<<(unsigned)ctas, ATT_THREADS, Cfg::SMEM_BYTES, s>>>(tq, tk, tv, p);
+  kern<<<(unsigned)ctas, ATT_THREADS, Cfg::SMEM_BYTES, s>>>(tk, tv, p);
   return check_launch("sparse_attn_kernel");
 }
 
@@ -554,7 +574,7 @@ extern "C" int paro_sparse_attn(const int8_t* q8, const int8_t* k8, const uint16
                PARO_EALIGN, "paro_sparse_attn: output strides must be multiples of 8 elements");
   PARO_REQUIRE(sm_scale > 0.f, PARO_EINVAL, "paro_sparse_attn: sm_scale must be positive");
   AttnParams p;
-  p.q_scale = q_scale; p.k_scale = k_scale; p.v_scale = v_scale; p.vm = vm;
+  p.q8 = q8; p.q_scale = q_scale; p.k_scale = k_scale; p.v_scale = v_scale; p.vm = vm;
   p.pair_ptr = pair_ptr; p.pair_ent = pair_ent; p.inv_idx = inv_idx;
   p.out = out; p.lse = lse; p.status = status;
   p.osb = out_stride_b; p.osh = out_stride_h; p.osn = out_stride_n;
