@@ -140,7 +140,8 @@ int paro_plan_fill(const uint8_t* mask, int slices, int nbq, int nbk,
  * permute_attn_out (cogvideox.py:64-110).
  *   q8,k8: contiguous int8 [B,H,N,D]; q_scale [B,H,ceil(N/64)*(64/q_group)], k_scale
  *   [B,H,ceil(N/64)]; v16: fp16 [B,H,D,ceil64(N)] (e4m3 values), v_scale/vm [B,H,D] (vm may
- *   be NULL); pair_ptr/pair_ent from paro_plan_*, plan_slices = H (shared by the batch) or B*H;
+ *   be NULL); row_ptr/cols from paro_plan_* (per q-block ascending kept k-blocks), plan_slices = H
+ *   (shared by the batch) or B*H;
  *   inv_idx (nullable): table of paro_build_perm_index -- output row n_text+j of head h is
  *   stored at token n_text+inv_idx[h][j]; out: [B,H,N,D] through element strides; lse
  *   (nullable) fp32 [B,H,N] in output token order, natural log; status: int32[4] device
@@ -150,7 +151,7 @@ int paro_plan_fill(const uint8_t* mask, int slices, int nbq, int nbk,
 int paro_sparse_attn(const int8_t* q8, const int8_t* k8, const uint16_t* v16,
                      const float* q_scale, int q_group, const float* k_scale,
                      const float* v_scale, const float* vm,
-                     const int32_t* pair_ptr, const int32_t* pair_ent, int plan_slices,
+                     const int32_t* row_ptr, const int32_t* cols, int plan_slices,
                      const int32_t* inv_idx, int n_text,
                      void* out, int out_dtype,
                      int64_t out_stride_b, int64_t out_stride_h, int64_t out_stride_n,

@@ -1,17 +1,20 @@
 // Block-sparse attention over kept 64x64 blocks for sm_100a.
 //
 // Work item (one CTA): a PAIR of adjacent 64-row q-blocks of one (batch, head), i.e. a 128-row
-// tile -- the native tcgen05.mma M -- walking the union of the two blocks' kept k-blocks.  Each list
-// entry says which of the two halves keeps the block; the half that does not is given P = 0.
+// tile -- the native tcgen05.mma M.  The two halves walk their OWN lists of kept k-blocks in
+// lock step: in step i the upper half works on its i-th kept block and the lower half on its i-th
+// kept block.  Each MMA is issued with the query tile of all 128 rows but with a lane mask that
+// keeps it from writing the other half's accumulator rows, so both halves always have work (all
+// four SM sub-partitions run exponentials) and nothing is computed for blocks that are not kept.
 //
 //   warps 0-7   softmax + epilogue.  Row r of the tile is shared by two threads: warp w (< 4)
 //               takes score columns 0-31, warp w+4 columns 32-63 (both may touch TMEM lane
 //               quadrant w).  Online softmax in fp32 (base 2, lazy rescaling); the two threads
-//               exchange their partial row maximum through shared memory.  P is written back over S
-//               in TMEM as fp16; the epilogue stores O/l * v_scale + vm at the row's un-permuted
-//               position.  These warps take the registers the others give up.
-//   warp 8      TMA producer for the K ring (int8 tiles, freed when Q.K^T is done)
-//   warp 9      TMA producer for the V^T ring (fp16 tiles, freed when P.V is done)
+//               exchange their partial row maximum through shared memory.  P is written to TMEM as
+//               fp16; the epilogue stores O/l * v_scale + vm at the row's un-permuted position.
+//               These warps take the registers the others give up.
+//   warp 8      TMA producer for the K ring (int8 tiles, freed when their Q.K^T is done)
+//   warp 9      TMA producer for the V^T ring (fp16 tiles, freed when their P.V is done)
 //   warp 10     owns TMEM; one lane issues S = Q.K^T (kind::i8, int32 accumulators in TMEM) and
 //               O += P.V (kind::f16, P read from TMEM, fp32 accumulators in TMEM)
 //   warp 11     idle (completes the third warpgroup)
@@ -19,9 +22,10 @@
 // TMEM (256 columns per CTA): S [0,64) int32 scores, P [64,96) fp16 probabilities, Q [96,128) the
 // int8 query tile (A operand of Q.K^T read from TMEM, so it is not re-read from shared memory for
 // every k-block), O [128,128+D) fp32.  The softmax threads release S as soon as they hold the scores
-// in registers, so Q.K^T of tile i+1 overlaps the exponentials of tile i, and P.V of tile i overlaps
-// the softmax of tile i+1; two CTAs share an SM so that one CTA's softmax overlaps the other's MMAs.  Every wait is bounded: on expiry the
-// CTA records a code in the status words, raises a shared abort flag and unwinds (TMEM freed).
+// in registers, so Q.K^T of step i+1 overlaps the exponentials of step i, and P.V of step i overlaps
+// the softmax of step i+1; two CTAs share an SM so that one CTA's softmax overlaps the other's MMAs.
+// Every wait is bounded: on expiry the CTA records a code in the status words, raises a shared
+// abort flag and unwinds (TMEM freed).
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -57,8 +61,8 @@ struct AttnParams {
   const float* k_scale;
   const float* v_scale;
   const float* vm;
-  const int32_t* pair_ptr;
-  const int32_t* pair_ent;
+  const int32_t* row_ptr;
+  const int32_t* cols;
   const int32_t* inv_idx;
   void* out;
   float* lse;
@@ -151,9 +155,14 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int bh = blockIdx.x / p.npairs, pair = blockIdx.x % p.npairs;
   const int slice = bh % p.plan_slices;
-  const int ent0 = p.pair_ptr[slice * p.npairs + pair];
-  const int n_ent = p.pair_ptr[slice * p.npairs + pair + 1] - ent0;
-  const int32_t* ent = p.pair_ent + ent0;
+  // the two halves' lists (ascending kept k-blocks of q-blocks 2*pair and 2*pair+1)
+  const int row_a = slice * p.nb + 2 * pair;
+  const int a0 = p.row_ptr[row_a], n_a = p.row_ptr[row_a + 1] - a0;
+  const bool has_b = 2 * pair + 1 < p.nb;
+  const int b0 = has_b ? p.row_ptr[row_a + 1] : 0, n_b = has_b ? p.row_ptr[row_a + 2] - b0 : 0;
+  const int n_steps = max(n_a, n_b), n_min = min(n_a, n_b);
+  // position of half h's tile of step i in the order in which tiles pass through the rings
+  auto seq = [&](int i, int h) { return i < n_min ? 2 * i + h : 2 * n_min + (i - n_min); };
 
   if (threadIdx.x == 0) {
     mbar_init(bar_q, 4);
@@ -183,66 +192,102 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
   if (warp >= 8) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 48;");
     if (warp == 8 && lane == 0) {
-      // ---------------------------------------------------------------- TMA producer: Q, K ring
+      // ---------------------------------------------------------------- TMA producer: K ring
       tma_prefetch_desc(&tm_k);
-      for (int i = 0; i < n_ent; ++i) {
-        const int st = i % KST, use = i / KST;
-        const int kb = ent[i] >> 2;
-        if (use > 0) { ATT_WAIT(bar_qkdone + st, (use - 1) & 1, 1, i) }
+      bool ok = true;
+      for (int i = 0; i < n_steps && ok; ++i) {
+        for (int h = 0; h < 2; ++h) {
+          if (i >= (h ? n_b : n_a)) continue;
+          const int t = seq(i, h), st = t % KST, use = t / KST;
+          const int kb = p.cols[(h ? b0 : a0) + i];
+          if (use > 0 && !mbar_wait_bounded(bar_qkdone + st, (use - 1) & 1, abort_flag, WAIT_LIMIT)) {
+            report_timeout(p, abort_flag, 1, i);
+            ok = false;
+            break;
+          }
 #ifdef PARO_ABL_NO_TMA
-        if (use > 0) { mbar_arrive(bar_kfull + st); continue; }
+          if (use > 0) { mbar_arrive(bar_kfull + st); continue; }
 #endif
-        mbar_arrive_expect_tx(bar_kfull + st, Cfg::K_BYTES);
-        tma_load_3d(sK + st * Cfg::K_BYTES, &tm_k, 0, kb * 64, bh, bar_kfull + st);
+          mbar_arrive_expect_tx(bar_kfull + st, Cfg::K_BYTES);
+          tma_load_3d(sK + st * Cfg::K_BYTES, &tm_k, 0, kb * 64, bh, bar_kfull + st);
+        }
       }
     } else if (warp == 9 && lane == 0) {
       // ---------------------------------------------------------------- TMA producer: V ring
       tma_prefetch_desc(&tm_v);
-      for (int i = 0; i < n_ent; ++i) {
-        const int st = i % VST, use = i / VST;
-        const int kb = ent[i] >> 2;
-        if (use > 0) { ATT_WAIT(bar_pvdone + st, (use - 1) & 1, 9, i) }
+      bool ok = true;
+      for (int i = 0; i < n_steps && ok; ++i) {
+        for (int h = 0; h < 2; ++h) {
+          if (i >= (h ? n_b : n_a)) continue;
+          const int t = seq(i, h), st = t % VST, use = t / VST;
+          const int kb = p.cols[(h ? b0 : a0) + i];
+          if (use > 0 && !mbar_wait_bounded(bar_pvdone + st, (use - 1) & 1, abort_flag, WAIT_LIMIT)) {
+            report_timeout(p, abort_flag, 9, i);
+            ok = false;
+            break;
+          }
 #ifdef PARO_ABL_NO_TMA
-        if (use > 0) { mbar_arrive(bar_vfull + st); continue; }
+          if (use > 0) { mbar_arrive(bar_vfull + st); continue; }
 #endif
-        mbar_arrive_expect_tx(bar_vfull + st, Cfg::V_BYTES);
-        tma_load_3d(sV + st * Cfg::V_BYTES, &tm_v, kb * 64, 0, bh, bar_vfull + st);
+          mbar_arrive_expect_tx(bar_vfull + st, Cfg::V_BYTES);
+          tma_load_3d(sV + st * Cfg::V_BYTES, &tm_v, kb * 64, 0, bh, bar_vfull + st);
+        }
       }
     } else if (warp == 10 && lane == 0) {
       // ---------------------------------------------------------------- MMA issuer
       constexpr uint32_t IDESC_QK = instr_desc(2, 1, 1, 128, 64);  // s32 += s8 * s8
       constexpr uint32_t IDESC_PV = instr_desc(1, 0, 0, 128, D);   // f32 += f16 * f16
+      bool ok = true;
+      // scores of step i: one masked MMA group per half that still has blocks
       auto issue_qk = [&](int i) {
-        const uint64_t dK = smem_desc(smem_u32(sK + (i % KST) * Cfg::K_BYTES), D);
+        for (int h = 0; h < 2 && ok; ++h) {
+          if (i >= (h ? n_b : n_a)) continue;
+          const int t = seq(i, h), st = t % KST;
+          if (!mbar_wait_bounded(bar_kfull + st, (t / KST) & 1, abort_flag, WAIT_LIMIT)) {
+            report_timeout(p, abort_flag, 3, i);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint64_t dK = smem_desc(smem_u32(sK + st * Cfg::K_BYTES), D);
+          const uint32_t lo = h ? 0xffffffffu : 0u, hi = ~lo;   // lanes NOT written: the other half's rows
 #pragma unroll
-        for (int k = 0; k < D / 32; ++k)
-          mma_i8_ts(tS, tQ + 8 * k, desc_advance(dK, 32 * k), IDESC_QK, k > 0);
-        mma_commit(bar_qkdone + i % KST);
+          for (int k = 0; k < D / 32; ++k)
+            mma_i8_ts_masked(tS, tQ + 8 * k, desc_advance(dK, 32 * k), IDESC_QK, k > 0, lo, lo, hi, hi);
+          mma_commit(bar_qkdone + st);
+        }
       };
       do {
         ATT_WAIT(bar_q, 0, 2, -1)
-        if (n_ent == 0) break;
-        ATT_WAIT(bar_kfull + 0, 0, 3, 0)
+        if (n_steps == 0) break;
         tc_fence_after();
         issue_qk(0);
-        for (int i = 0; i < n_ent; ++i) {
-          const int st = i % VST;
-          if (i + 1 < n_ent) {
-            ATT_WAIT(bar_kfull + (i + 1) % KST, ((i + 1) / KST) & 1, 3, i + 1)
-            ATT_WAIT(bar_sfree, i & 1, 10, i)     // the scores of tile i are in registers: S may be overwritten
-            tc_fence_after();
+        for (int i = 0; i < n_steps && ok; ++i) {
+          if (i + 1 < n_steps) {
+            ATT_WAIT(bar_sfree, i & 1, 10, i)     // the scores of step i are in registers: S may be overwritten
             issue_qk(i + 1);
+            if (!ok) break;
           }
 #ifndef PARO_ABL_NO_PWAIT
           ATT_WAIT(bar_pready, i & 1, 4, i)
 #endif
-          ATT_WAIT(bar_vfull + st, (i / VST) & 1, 5, i)
-          tc_fence_after();
-          const uint64_t dV = smem_desc(smem_u32(sV + st * Cfg::V_BYTES), 128);
+          for (int h = 0; h < 2; ++h) {
+            if (i >= (h ? n_b : n_a)) continue;
+            const int t = seq(i, h), st = t % VST;
+            if (!mbar_wait_bounded(bar_vfull + st, (t / VST) & 1, abort_flag, WAIT_LIMIT)) {
+              report_timeout(p, abort_flag, 5, i);
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            const uint64_t dV = smem_desc(smem_u32(sV + st * Cfg::V_BYTES), 128);
+            const uint32_t lo = h ? 0xffffffffu : 0u, hi = ~lo;
 #pragma unroll
-          for (int k = 0; k < 4; ++k)
-            mma_f16_ts(tO, tP + 8 * k, desc_advance(dV, 32 * k), IDESC_PV, (i > 0 || k > 0) ? 1u : 0u);
-          mma_commit(bar_pvdone + st);
+            for (int k = 0; k < 4; ++k)
+              mma_f16_ts_masked(tO, tP + 8 * k, desc_advance(dV, 32 * k), IDESC_PV, (i > 0 || k > 0) ? 1u : 0u, lo, lo,
+                                hi, hi);
+            mma_commit(bar_pvdone + st);
+          }
         }
       } while (false);
     }
@@ -254,6 +299,8 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
     const int r = qd * 32 + lane;            // row inside the 128-row tile
     const int half = qd >> 1;                // which q-block of the pair
     const uint32_t lane_off = (uint32_t)(qd * 32) << 16;
+    const int n_mine = half ? n_b : n_a;
+    const int32_t* my_cols = p.cols + (half ? b0 : a0);
     if (threadIdx.x < D) {
       s_vscale[threadIdx.x] = p.v_scale[(size_t)bh * D + threadIdx.x];
       s_vm[threadIdx.x] = p.vm ? p.vm[(size_t)bh * D + threadIdx.x] : 0.f;
@@ -280,59 +327,61 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
     const float rowscale = (tok < p.N ? p.q_scale[(size_t)bh * per_bh + tok / p.q_group] : 0.f) * p.scale_log2;
     float m = -INFINITY, l = 0.f;   // l: this thread's share of the row sum
     bool ok = true;
-    // A parity wait can only tell "the phase before the current one is over", so every waiter
-    // consumes every completion of a barrier in order.  The softmax threads therefore wait for the
-    // P.V of tile i-1 during tile i -- early if O has to be rescaled, otherwise after the exponentials,
-    // when it has long completed and costs nothing -- and for the last one in the epilogue.
-    auto consume_pv = [&](int i) {   // P.V of tile i-1
-#ifdef PARO_ABL_FREE_RUN
-      return true;
-#endif
-      const bool good = __all_sync(0xffffffffu, mbar_wait_bounded(bar_pvdone + (i - 1) % VST, ((i - 1) / VST) & 1,
-                                                                  abort_flag, WAIT_LIMIT));
-      if (!good) report_timeout(p, abort_flag, 7, i);
+    // A parity wait can only tell "the phase before the current one is over"; a waiter may skip
+    // phases of a ring barrier only because the rings are at least three deep and tiles complete
+    // in order, so the barrier is never more than one phase away from the one waited for.
+    auto wait_tile = [&](uint64_t* bars, int depth, int t, int code, int i) {
+      const bool good = __all_sync(0xffffffffu, mbar_wait_bounded(bars + t % depth, (t / depth) & 1, abort_flag, WAIT_LIMIT));
+      if (!good) report_timeout(p, abort_flag, code, i);
       tc_fence_after();
       return good;
     };
     const float* kscale_bh = p.k_scale + (size_t)bh * p.nb;
-    int e_next = n_ent > 0 ? ent[0] : 0;
-    float ks_next = n_ent > 0 ? kscale_bh[e_next >> 2] : 0.f;
-    int n_kept = 0;                 // kept tiles seen by this row: selects the exchange buffer
-    for (int i = 0; i < n_ent; ++i) {
-      const int e = e_next;
+    int kb_next = n_mine > 0 ? my_cols[0] : 0;
+    float ks_next = n_mine > 0 ? kscale_bh[kb_next] : 0.f;
+    for (int i = 0; i < n_steps; ++i) {
+      if (i >= n_mine) {
+        // this half has no blocks left: keep the step barriers going, but never arrive for step i
+        // before step i-1 of the P barrier has completed (an early arrival would be counted there)
+        if (i > 0) {
+          ok = __all_sync(0xffffffffu, mbar_wait_bounded(bar_pready, (i - 1) & 1, abort_flag, WAIT_LIMIT));
+          if (!ok) {
+            report_timeout(p, abort_flag, 11, i);
+            break;
+          }
+        }
+        // the last P.V of this half is awaited now, while its ring barrier is still within one
+        // phase (in the epilogue the other half's later tiles would have moved it on)
+        if (i == n_mine && n_mine > 0) {
+          ok = wait_tile(bar_pvdone, VST, seq(n_mine - 1, half), 8, i);
+          if (!ok) break;
+        }
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(bar_sfree);
+          mbar_arrive(bar_pready);
+        }
+        continue;
+      }
+      const int kb = kb_next;
       const float kscale = ks_next;
-      const int kb = e >> 2;
-      const bool keep = (e >> half) & 1;
-      if (i + 1 < n_ent) {   // fetched one tile ahead so that the loads are off the critical path
-        e_next = ent[i + 1];
-        ks_next = kscale_bh[e_next >> 2];
+      if (i + 1 < n_mine) {   // fetched one step ahead so that the loads are off the critical path
+        kb_next = my_cols[i + 1];
+        ks_next = kscale_bh[kb_next];
       }
 #ifndef PARO_ABL_FREE_RUN
-      ok = __all_sync(0xffffffffu, mbar_wait_bounded(bar_qkdone + i % KST, (i / KST) & 1, abort_flag, WAIT_LIMIT));
-      if (!ok) {
-        report_timeout(p, abort_flag, 6, i);
-        break;
-      }
+      ok = wait_tile(bar_qkdone, KST, seq(i, half), 6, i);
+      if (!ok) break;
 #endif
-      tc_fence_after();
       uint32_t pk[16];
       bool pv_consumed = (i == 0);
-#ifdef PARO_ABL_NO_EXP
-      if (false) {
-#else
-      if (keep) {
-#endif
+      {
         float f[32];
         {
           uint32_t s[32];
-#ifdef PARO_ABL_NO_LD
-#pragma unroll
-          for (int j = 0; j < 32; ++j) s[j] = (uint32_t)(j * lane + i);
-#else
           tmem_ld32(tS + lane_off + 32 * ch, s);
           tmem_wait_ld();
-#endif
-          // the scores are in registers: let the issuer overwrite S with the next tile's
+          // the scores are in registers: let the issuer overwrite S with the next step's
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(bar_sfree);
@@ -358,16 +407,11 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
         }
         const float my_max = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
         // the row's other 32 columns belong to the thread of warp (w ^ 4) with the same lane
-        float* xb = s_xchg + (n_kept & 1) * 256;
+        float* xb = s_xchg + (i & 1) * 256;
         const float sc = rowscale * kscale;
-#ifdef PARO_ABL_NO_XCHG
-        const float mx = my_max * sc + xb[0];
-#else
         xb[ch * 128 + r] = my_max;
         named_barrier(2 + qd, 64);
         const float mx = fmaxf(my_max, xb[(ch ^ 1) * 128 + r]) * sc;
-#endif
-        ++n_kept;
         float alpha = 1.f;
         bool resc = false;
         if (mx > m + RESCALE_TAU) {
@@ -376,10 +420,10 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
           m = mx;
           l *= alpha;
         }
-        if (__any_sync(0xffffffffu, resc)) {  // O may only be touched once the previous P.V has landed
+        if (__any_sync(0xffffffffu, resc)) {  // O may only be touched once this half's previous P.V has landed
           if (!pv_consumed) {
             pv_consumed = true;
-            ok = consume_pv(i);
+            ok = wait_tile(bar_pvdone, VST, seq(i - 1, half), 7, i);
             if (!ok) break;
           }
 #pragma unroll
@@ -412,20 +456,15 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
         float sa, sb;
         unpack2(add2(sum2[0], sum2[1]), sa, sb);
         l += sa + sb;
-      } else {
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar_sfree);
-#pragma unroll
-        for (int j = 0; j < 16; ++j) pk[j] = 0u;
       }
+      // P of this half is rewritten only after the P.V that read its previous contents has finished
+      // (that P.V was issued a whole softmax ago, so this wait normally returns at once)
       if (!pv_consumed) {
-        ok = consume_pv(i);
+        ok = wait_tile(bar_pvdone, VST, seq(i - 1, half), 7, i);
         if (!ok) break;
       }
-#ifndef PARO_ABL_NO_ST
       tmem_st16(tP + lane_off + 16 * ch, pk);   // fp16 P: two values per 32-bit column
       tmem_wait_st();
-#endif
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_pready);   // one arrival per warp
@@ -433,18 +472,9 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
 
     // epilogue (the TMEM loads are warp-collective: every lane of the warp executes them, rows past
     // the end of the sequence only skip the store)
-#ifdef PARO_ABL_FREE_RUN
-    if (false) {
-#else
-    if (ok && n_ent > 0) {
-#endif
-      ok = __all_sync(0xffffffffu, mbar_wait_bounded(bar_pvdone + (n_ent - 1) % VST, ((n_ent - 1) / VST) & 1,
-                                                     abort_flag, WAIT_LIMIT));
-      if (!ok) report_timeout(p, abort_flag, 8, n_ent);
-      tc_fence_after();
-    }
+    if (ok && n_mine > 0 && n_mine == n_steps) ok = wait_tile(bar_pvdone, VST, seq(n_mine - 1, half), 8, n_mine);
     // row sum = both threads' shares (reached by every softmax thread, also after a failed wait)
-    float* xl = s_xchg + 512 - 256;   // second buffer is free again only after the loop: use a barrier first
+    float* xl = s_xchg;
     named_barrier(1, ATT_SOFTMAX_THREADS);
     xl[ch * 128 + r] = l;
     named_barrier(1, ATT_SOFTMAX_THREADS);
@@ -460,7 +490,7 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
 #pragma unroll
       for (int c = 0; c < D / 64; ++c) {
         uint32_t o[32];
-        if (n_ent > 0) {
+        if (n_mine > 0) {
           tmem_ld32(tO + lane_off + (uint32_t)(ch * (D / 2) + 32 * c), o);
           tmem_wait_ld();
         } else {
@@ -471,10 +501,10 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
           const int d0 = ch * (D / 2) + 32 * c + 2 * j;
-          const float a0 = l > 0.f ? fmaf(__uint_as_float(o[2 * j]) * inv_l, s_vscale[d0], s_vm[d0]) : 0.f;
-          const float a1 = l > 0.f ? fmaf(__uint_as_float(o[2 * j + 1]) * inv_l, s_vscale[d0 + 1], s_vm[d0 + 1]) : 0.f;
-          OutT t[2] = {F16Traits<OutT>::from_float(a0), F16Traits<OutT>::from_float(a1)};
-          w[j] = *reinterpret_cast<const uint32_t*>(t);
+          const float a0f = l > 0.f ? fmaf(__uint_as_float(o[2 * j]) * inv_l, s_vscale[d0], s_vm[d0]) : 0.f;
+          const float a1f = l > 0.f ? fmaf(__uint_as_float(o[2 * j + 1]) * inv_l, s_vscale[d0 + 1], s_vm[d0 + 1]) : 0.f;
+          OutT t2[2] = {F16Traits<OutT>::from_float(a0f), F16Traits<OutT>::from_float(a1f)};
+          w[j] = *reinterpret_cast<const uint32_t*>(t2);
         }
         if (live) {
 #pragma unroll
@@ -553,13 +583,13 @@ using namespace paro;
 extern "C" int paro_sparse_attn(const int8_t* q8, const int8_t* k8, const uint16_t* v16,
                                 const float* q_scale, int q_group, const float* k_scale,
                                 const float* v_scale, const float* vm,
-                                const int32_t* pair_ptr, const int32_t* pair_ent, int plan_slices,
+                                const int32_t* row_ptr, const int32_t* cols, int plan_slices,
                                 const int32_t* inv_idx, int n_text,
                                 void* out, int out_dtype,
                                 int64_t out_stride_b, int64_t out_stride_h, int64_t out_stride_n,
                                 float* lse, int B, int H, int N, int D, float sm_scale,
                                 int32_t* status, paro_stream_t stream) {
-  PARO_REQUIRE(q8 && k8 && v16 && q_scale && k_scale && v_scale && pair_ptr && pair_ent && out && status, PARO_EINVAL,
+  PARO_REQUIRE(q8 && k8 && v16 && q_scale && k_scale && v_scale && row_ptr && cols && out && status, PARO_EINVAL,
                "paro_sparse_attn: null pointer");
   PARO_REQUIRE(B > 0 && H > 0 && N > 0, PARO_ESHAPE, "paro_sparse_attn: empty problem");
   PARO_REQUIRE(D == 64 || D == 128, PARO_ESHAPE, "paro_sparse_attn: head_dim %d unsupported (64 or 128)", D);
@@ -575,7 +605,7 @@ extern "C" int paro_sparse_attn(const int8_t* q8, const int8_t* k8, const uint16
   PARO_REQUIRE(sm_scale > 0.f, PARO_EINVAL, "paro_sparse_attn: sm_scale must be positive");
   AttnParams p;
   p.q8 = q8; p.q_scale = q_scale; p.k_scale = k_scale; p.v_scale = v_scale; p.vm = vm;
-  p.pair_ptr = pair_ptr; p.pair_ent = pair_ent; p.inv_idx = inv_idx;
+  p.row_ptr = row_ptr; p.cols = cols; p.inv_idx = inv_idx;
   p.out = out; p.lse = lse; p.status = status;
   p.osb = out_stride_b; p.osh = out_stride_h; p.osn = out_stride_n;
   p.plan_slices = plan_slices; p.q_group = q_group; p.n_text = n_text;
