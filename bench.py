@@ -213,6 +213,10 @@ def main():
     plan = pb.compact_plan(mask_all[h0:h1].to(dev))
     pplan = pb.PermutePlan({"permute": orders.reshape(1, -1)}, wl["grid"], dev)
     rope = pb.rope_tables(wl["grid"], D, wl["family"], device=dev)
+    cnt = (plan.row_ptr[1:] - plan.row_ptr[:-1]).reshape(plan.slices, nb)
+    if nb % 2:
+        cnt = torch.cat([cnt, torch.zeros(plan.slices, 1, dtype=cnt.dtype, device=dev)], dim=1)
+    steps_local = int(cnt.reshape(plan.slices, -1, 2).amax(dim=-1).sum().item()) * B   # lock-step walk length
     kept_local = plan.kept_blocks * B
     kept_total = int(mask_all.sum()) * B
     flops_block = 4 * 64 * 64 * D
@@ -298,7 +302,7 @@ def main():
         "config": {"workload": args.workload, "B": B, "H": H, "D": D, "N": N, "grid_fhw": list(wl["grid"]),
                    "n_text": n_text, "block": 64, "nominal_density": wl["density"],
                    "measured_density": kept_total / (B * H * nb * nb), "kept_blocks": kept_total,
-                   "pair_tiles_rank0": plan.pair_tiles * B, "partition": f"{world} x heads", "in_dtype": "bf16",
+                   "lockstep_steps_rank0": steps_local, "partition": f"{world} x heads", "in_dtype": "bf16",
                    "l2": "inputs larger than L2 (no flush needed)"},
         "attention_kernel_ms": attn_ms_max,
         "pre_attention_ms": ms_per_step - attn_ms_max,

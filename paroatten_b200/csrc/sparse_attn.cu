@@ -15,9 +15,8 @@
 //               These warps take the registers the others give up.
 //   warp 8      TMA producer for the K ring (int8 tiles, freed when their Q.K^T is done)
 //   warp 9      TMA producer for the V^T ring (fp16 tiles, freed when their P.V is done)
-//   warp 10     owns TMEM; one lane issues S = Q.K^T (kind::i8, int32 accumulators in TMEM) and
-//               O += P.V (kind::f16, P read from TMEM, fp32 accumulators in TMEM)
-//   warp 11     idle (completes the third warpgroup)
+//   warp 10     owns TMEM; one lane issues S = Q.K^T (kind::i8, A = Q from TMEM, int32 accumulators)
+//   warp 11     one lane issues O += P.V (kind::f16, A = P from TMEM, fp32 accumulators in TMEM)
 //
 // TMEM (256 columns per CTA): S [0,64) int32 scores, P [64,96) fp16 probabilities, Q [96,128) the
 // int8 query tile (A operand of Q.K^T read from TMEM, so it is not re-read from shared memory for
@@ -115,6 +114,18 @@ __device__ __forceinline__ void report_timeout(const AttnParams& p, volatile int
   }
   *abort_flag = 1;
 }
+
+// Optional cycle accounting of one softmax warp (diagnostic builds only: -DPARO_ATTN_TRACE).
+#ifdef PARO_ATTN_TRACE
+__device__ unsigned long long g_trace[16];
+#define TR_DECL long long tr_acc[6] = {0, 0, 0, 0, 0, 0}, tr_t = 0
+#define TR_MARK tr_t = clock64()
+#define TR_ACC(k) do { const long long n__ = clock64(); tr_acc[k] += n__ - tr_t; tr_t = n__; } while (0)
+#else
+#define TR_DECL do { } while (0)
+#define TR_MARK do { } while (0)
+#define TR_ACC(k) do { } while (0)
+#endif
 
 #define ATT_WAIT(bar, parity, where, iter)                                   \
   if (!mbar_wait_bounded((bar), (parity), abort_flag, WAIT_LIMIT)) {         \
@@ -234,62 +245,59 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
         }
       }
     } else if (warp == 10 && lane == 0) {
-      // ---------------------------------------------------------------- MMA issuer
+      // ---------------------------------------------------------------- MMA issuer: S = Q.K^T
+      // (the two issuers are separate threads so that a P.V group waiting for room in the tensor
+      // queue does not hold back the next scores, and vice versa)
       constexpr uint32_t IDESC_QK = instr_desc(2, 1, 1, 128, 64);  // s32 += s8 * s8
-      constexpr uint32_t IDESC_PV = instr_desc(1, 0, 0, 128, D);   // f32 += f16 * f16
-      bool ok = true;
-      // scores of step i: one masked MMA group per half that still has blocks
-      auto issue_qk = [&](int i) {
-        for (int h = 0; h < 2 && ok; ++h) {
-          if (i >= (h ? n_b : n_a)) continue;
-          const int t = seq(i, h), st = t % KST;
-          if (!mbar_wait_bounded(bar_kfull + st, (t / KST) & 1, abort_flag, WAIT_LIMIT)) {
-            report_timeout(p, abort_flag, 3, i);
-            ok = false;
-            break;
-          }
-          tc_fence_after();
-          const uint64_t dK = smem_desc(smem_u32(sK + st * Cfg::K_BYTES), D);
-          const uint32_t lo = h ? 0xffffffffu : 0u, hi = ~lo;   // lanes NOT written: the other half's rows
-#pragma unroll
-          for (int k = 0; k < D / 32; ++k)
-            mma_i8_ts_masked(tS, tQ + 8 * k, desc_advance(dK, 32 * k), IDESC_QK, k > 0, lo, lo, hi, hi);
-          mma_commit(bar_qkdone + st);
-        }
-      };
       do {
         ATT_WAIT(bar_q, 0, 2, -1)
-        if (n_steps == 0) break;
-        tc_fence_after();
-        issue_qk(0);
+        bool ok = true;
         for (int i = 0; i < n_steps && ok; ++i) {
-          if (i + 1 < n_steps) {
-            ATT_WAIT(bar_sfree, i & 1, 10, i)     // the scores of step i are in registers: S may be overwritten
-            issue_qk(i + 1);
-            if (!ok) break;
-          }
-#ifndef PARO_ABL_NO_PWAIT
-          ATT_WAIT(bar_pready, i & 1, 4, i)
-#endif
-          for (int h = 0; h < 2; ++h) {
+          if (i > 0) { ATT_WAIT(bar_sfree, (i - 1) & 1, 10, i) }   // scores of step i-1 are in registers
+          for (int h = 0; h < 2; ++h) {   // one lane-masked MMA group per half that still has blocks
             if (i >= (h ? n_b : n_a)) continue;
-            const int t = seq(i, h), st = t % VST;
-            if (!mbar_wait_bounded(bar_vfull + st, (t / VST) & 1, abort_flag, WAIT_LIMIT)) {
-              report_timeout(p, abort_flag, 5, i);
+            const int t = seq(i, h), st = t % KST;
+            if (!mbar_wait_bounded(bar_kfull + st, (t / KST) & 1, abort_flag, WAIT_LIMIT)) {
+              report_timeout(p, abort_flag, 3, i);
               ok = false;
               break;
             }
             tc_fence_after();
-            const uint64_t dV = smem_desc(smem_u32(sV + st * Cfg::V_BYTES), 128);
-            const uint32_t lo = h ? 0xffffffffu : 0u, hi = ~lo;
+            const uint64_t dK = smem_desc(smem_u32(sK + st * Cfg::K_BYTES), D);
+            const uint32_t lo = h ? 0xffffffffu : 0u, hi = ~lo;   // lanes NOT written: the other half's rows
 #pragma unroll
-            for (int k = 0; k < 4; ++k)
-              mma_f16_ts_masked(tO, tP + 8 * k, desc_advance(dV, 32 * k), IDESC_PV, (i > 0 || k > 0) ? 1u : 0u, lo, lo,
-                                hi, hi);
-            mma_commit(bar_pvdone + st);
+            for (int k = 0; k < D / 32; ++k)
+              mma_i8_ts_masked(tS, tQ + 8 * k, desc_advance(dK, 32 * k), IDESC_QK, k > 0, lo, lo, hi, hi);
+            mma_commit(bar_qkdone + st);
           }
         }
       } while (false);
+    } else if (warp == 11 && lane == 0) {
+      // ---------------------------------------------------------------- MMA issuer: O += P.V
+      constexpr uint32_t IDESC_PV = instr_desc(1, 0, 0, 128, D);   // f32 += f16 * f16
+      bool ok = true;
+      for (int i = 0; i < n_steps && ok; ++i) {
+#ifndef PARO_ABL_NO_PWAIT
+        ATT_WAIT(bar_pready, i & 1, 4, i)
+#endif
+        for (int h = 0; h < 2; ++h) {
+          if (i >= (h ? n_b : n_a)) continue;
+          const int t = seq(i, h), st = t % VST;
+          if (!mbar_wait_bounded(bar_vfull + st, (t / VST) & 1, abort_flag, WAIT_LIMIT)) {
+            report_timeout(p, abort_flag, 5, i);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint64_t dV = smem_desc(smem_u32(sV + st * Cfg::V_BYTES), 128);
+          const uint32_t lo = h ? 0xffffffffu : 0u, hi = ~lo;
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            mma_f16_ts_masked(tO, tP + 8 * k, desc_advance(dV, 32 * k), IDESC_PV, (i > 0 || k > 0) ? 1u : 0u, lo, lo, hi,
+                              hi);
+          mma_commit(bar_pvdone + st);
+        }
+      }
     }
   } else {
     // ------------------------------------------------------------------ softmax + epilogue
@@ -339,7 +347,9 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
     const float* kscale_bh = p.k_scale + (size_t)bh * p.nb;
     int kb_next = n_mine > 0 ? my_cols[0] : 0;
     float ks_next = n_mine > 0 ? kscale_bh[kb_next] : 0.f;
+    TR_DECL;
     for (int i = 0; i < n_steps; ++i) {
+      TR_MARK;
       if (i >= n_mine) {
         // this half has no blocks left: keep the step barriers going, but never arrive for step i
         // before step i-1 of the P barrier has completed (an early arrival would be counted there)
@@ -373,6 +383,7 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
       ok = wait_tile(bar_qkdone, KST, seq(i, half), 6, i);
       if (!ok) break;
 #endif
+      TR_ACC(0);
       uint32_t pk[16];
       bool pv_consumed = (i == 0);
       {
@@ -381,6 +392,7 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
           uint32_t s[32];
           tmem_ld32(tS + lane_off + 32 * ch, s);
           tmem_wait_ld();
+          TR_ACC(1);
           // the scores are in registers: let the issuer overwrite S with the next step's
           tc_fence_before();
           __syncwarp();
@@ -406,6 +418,7 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
           }
         }
         const float my_max = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+        TR_ACC(2);
         // the row's other 32 columns belong to the thread of warp (w ^ 4) with the same lane
         float* xb = s_xchg + (i & 1) * 256;
         const float sc = rowscale * kscale;
@@ -438,6 +451,7 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
           }
           tmem_wait_st();
         }
+        TR_ACC(3);
         const uint64_t sc2 = pack2(sc, sc), negm2 = pack2(-m, -m);
         uint64_t sum2[2] = {0ull, 0ull};
 #pragma unroll
@@ -456,6 +470,7 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
         float sa, sb;
         unpack2(add2(sum2[0], sum2[1]), sa, sb);
         l += sa + sb;
+        TR_ACC(4);
       }
       // P of this half is rewritten only after the P.V that read its previous contents has finished
       // (that P.V was issued a whole softmax ago, so this wait normally returns at once)
@@ -468,7 +483,15 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_pready);   // one arrival per warp
+      TR_ACC(5);
     }
+#ifdef PARO_ATTN_TRACE
+    if (lane == 0 && warp == 0) {
+      for (int k = 0; k < 6; ++k) atomicAdd(&g_trace[k], (unsigned long long)tr_acc[k]);
+      atomicAdd(&g_trace[6], (unsigned long long)n_mine);
+      atomicAdd(&g_trace[7], (unsigned long long)n_steps);
+    }
+#endif
 
     // epilogue (the TMEM loads are warp-collective: every lane of the warp executes them, rows past
     // the end of the sequence only skip the store)

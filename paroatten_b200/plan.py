@@ -41,9 +41,9 @@ class CompactPlan:
     row_ptr: torch.Tensor    # int32 [slices*nbq + 1]
     cols: torch.Tensor       # int32 [kept]: ascending k-block ids per q-block
     pair_ptr: torch.Tensor   # int32 [slices*ceil(nbq/2) + 1]
-    pair_ent: torch.Tensor   # int32: kb*4 + flags per pair of adjacent q-blocks
+    pair_ent: torch.Tensor   # int32: kb*4 + flags per pair of adjacent q-blocks (merged walk; auxiliary)
     kept_blocks: int         # number of true entries of the mask
-    pair_tiles: int          # number of 128x64 tiles the attention kernel computes
+    pair_tiles: int          # size of the merged (union) walk over all q-block pairs
 
 
 def compact_plan(mask: torch.Tensor) -> CompactPlan:
