@@ -269,23 +269,27 @@ def main():
     # ---- end-to-end arm: host buffers, copies inside the timed region ------------------------
     e2e = None
     if not args.no_e2e:
+        # the public host-memory entry point: head groups pipelined over three streams, so the copy of
+        # group c+1 and the read-back of group c-1 overlap the kernels of group c
         hq, hk, hv = (t_.cpu().pin_memory() for t_ in (q, k, v))
         ho = torch.empty(out.shape, dtype=out.dtype).pin_memory()
-        dq, dk, dv = (torch.empty_like(t_) for t_ in (q, k, v))
+        pipe = pb.HostPipelinedAttention(orders_all[h0:h1], mask_all[h0:h1], (B, Hl, N, D), torch.bfloat16,
+                                         grid_fhw=wl["grid"], n_text=n_text, rope=rope,
+                                         heads_per_group=max(1, min(5, Hl)), device=dev)
 
         def e2e_step():
-            dq.copy_(hq, non_blocking=True)
-            dk.copy_(hk, non_blocking=True)
-            dv.copy_(hv, non_blocking=True)
-            ho.copy_(step(dq, dk, dv), non_blocking=True)
+            pipe(hq, hk, hv, ho)
         e2e_steps = max(3, min(args.steps, 10))
         for _ in range(3):
             e2e_step()
         e2e_ms = timed(e2e_step, e2e_steps) / e2e_steps
+        pb.check_status(dev)
+        same = bool(torch.equal(ho.to(dev), out))
         e2e = {"value": kept_total * flops_block / (e2e_ms * 1e-3) / 1e12, "unit": "TOPS", "ms_per_step": e2e_ms,
-               "h2d_bytes_per_step": 3 * q.numel() * 2 * world, "d2h_bytes_per_step": out.numel() * 2 * world,
-               "steps": e2e_steps}
-        del hq, hk, hv, ho, dq, dk, dv
+               "h2d_bytes_per_step": pipe.h2d_bytes * world, "d2h_bytes_per_step": pipe.d2h_bytes * world,
+               "steps": e2e_steps, "api": "paroatten_b200.HostPipelinedAttention (pinned host in, pinned host out)",
+               "matches_device_arm": same}
+        del hq, hk, hv, ho, pipe
 
     if rank != 0:
         if world > 1:
@@ -312,10 +316,10 @@ def main():
                      "frac": achieved / peak_i8,
                      "peak_note": f"2 x bf16_tflops_sustained of {pk['src']} peaks (dense INT8/FP8 rate); "
                                   f"the kernel's PV half runs at the fp16 rate, so its own ceiling is 4/3 x bf16",
-                     # DRAM bytes of one attention launch: ncu measured 593.4 MB on the 1.3B-480p shape
+                     # DRAM bytes of one attention launch: ncu measured 592.7 MB on the 1.3B-480p shape
                      # (profiles/sparse_attn_kernel_wan1p3b_480p.md), equal to the compulsory operand/output bytes;
                      # scaled here by B*H*N, to which those bytes are proportional
-                     "traffic": 593.4e6 * (B * Hl * N) / (2 * 12 * 32760) if D == 128 else None},
+                     "traffic": 592.7e6 * (B * Hl * N) / (2 * 12 * 32760) if D == 128 else None},
         "e2e": e2e,
     }
     if not args.no_cpu and world == 1:

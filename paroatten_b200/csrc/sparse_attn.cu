@@ -45,8 +45,12 @@ constexpr float RESCALE_TAU = 8.0f;         // rescale O only when the row max g
 
 template <int D> struct AttnCfg {
   // ring depths, sized so that exactly two CTAs fit an SM (TMEM allows no more)
-  static constexpr int K_STAGES = (D == 128) ? 5 : 8;
-  static constexpr int V_STAGES = (D == 128) ? 4 : 7;
+#ifndef PARO_ATT_KST128
+#define PARO_ATT_KST128 5
+#define PARO_ATT_VST128 4
+#endif
+  static constexpr int K_STAGES = (D == 128) ? PARO_ATT_KST128 : 8;
+  static constexpr int V_STAGES = (D == 128) ? PARO_ATT_VST128 : 7;
   static constexpr int K_BYTES = 64 * D;
   static constexpr int V_BYTES = D * 128;   // D rows of 64 fp16
   static constexpr int TILE_BYTES = K_STAGES * K_BYTES + V_STAGES * V_BYTES;

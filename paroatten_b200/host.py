@@ -1,0 +1,98 @@
+"""The path for activations that live in HOST memory.
+
+Every (batch, head) is independent, so a call whose q, k, v sit in pinned host memory can be cut
+into groups of heads and pipelined: while group c is computed, group c+1 is copied to the device
+and the result of group c-1 is copied back (PCIe carries both directions at once).  The per-group
+work is the ordinary device path (`core.paro_attention`), so results are bit-identical to a single
+device-resident call.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+
+from . import _lib
+from .core import paro_attention
+from .plan import CompactPlan, PermutePlan, compact_plan
+from .rope import RopeTables
+
+
+class HostPipelinedAttention:
+    """Set up once per (layer, timestep bin) -- the sparse plan is compacted per head group and
+    the staging buffers are allocated here -- then call it with pinned host tensors.
+
+    orders: int order ids [H]; mask: bool [H, nb, nb] (shared by the batch);
+    shape = (B, H, N, D) of the host tensors; heads_per_group: heads copied/computed at a time."""
+
+    def __init__(self, orders, mask: torch.Tensor, shape: Tuple[int, int, int, int], dtype, *, grid_fhw,
+                 n_text: int = 0, rope: Optional[RopeTables] = None, heads_per_group: int = 5, device=None,
+                 sm_scale: Optional[float] = None, smooth_k: bool = True, smooth_v: bool = True):
+        B, H, N, D = (int(x) for x in shape)
+        self.shape, self.dtype = (B, H, N, D), dtype
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.kw = dict(grid_fhw=tuple(int(g) for g in grid_fhw), n_text=int(n_text), rope=rope, sm_scale=sm_scale,
+                       smooth_k=smooth_k, smooth_v=smooth_v)
+        if mask.dim() != 3 or mask.shape[0] != H:
+            raise ValueError("mask must be [H, nb, nb]")
+        orders = torch.as_tensor(orders).to(torch.int32)
+        if orders.numel() != H:
+            raise ValueError("orders must hold one id per head")
+        g = max(1, min(int(heads_per_group), H))
+        self.groups: List[Tuple[int, int]] = [(h0, min(H, h0 + g)) for h0 in range(0, H, g)]
+        with torch.cuda.device(self.device):
+            self.plans: List[CompactPlan] = [compact_plan(mask[h0:h1].to(self.device)) for h0, h1 in self.groups]
+            self.pplans = [PermutePlan({"permute": orders[h0:h1].reshape(1, -1)}, self.kw["grid_fhw"], self.device)
+                           for h0, h1 in self.groups]
+            # two sets of staging buffers: one being filled while the other is consumed
+            self.stage = [[torch.empty(B, g, N, D, dtype=dtype, device=self.device) for _ in range(3)] for _ in range(2)]
+            self.s_in, self.s_comp, self.s_out = (torch.cuda.Stream(self.device) for _ in range(3))
+        self.h2d_bytes = 3 * B * H * N * D * torch.empty((), dtype=dtype).element_size()
+        self.d2h_bytes = self.h2d_bytes // 3
+
+    def __call__(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: Optional[torch.Tensor] = None):
+        B, H, N, D = self.shape
+        for t in (q, k, v):
+            if t.is_cuda or tuple(t.shape) != self.shape or t.dtype != self.dtype:
+                raise ValueError("q, k, v must be host tensors of the shape and dtype given at set-up")
+            if not t.is_pinned():
+                raise ValueError("q, k, v must be in pinned host memory (torch.Tensor.pin_memory())")
+        if out is None:
+            out = torch.empty(self.shape, dtype=self.dtype).pin_memory()
+        elif out.is_cuda or tuple(out.shape) != self.shape or not out.is_pinned():
+            raise ValueError("out must be a pinned host tensor of the same shape")
+        with torch.cuda.device(self.device):
+            main = torch.cuda.current_stream()
+            start = torch.cuda.Event()
+            start.record(main)
+            for s in (self.s_in, self.s_comp, self.s_out):
+                s.wait_event(start)
+            comp_done: List[torch.cuda.Event] = []
+            last_out = None
+            for c, (h0, h1) in enumerate(self.groups):
+                n = h1 - h0
+                bufs = [b[:, :n] for b in self.stage[c % 2]]
+                with torch.cuda.stream(self.s_in):
+                    if c >= 2:
+                        self.s_in.wait_event(comp_done[c - 2])       # the staging set is free again
+                    for dst, src in zip(bufs, (q, k, v)):
+                        for b in range(B):   # each (batch entry, head range) slab is contiguous on both sides
+                            dst[b].copy_(src[b, h0:h1], non_blocking=True)
+                    in_done = torch.cuda.Event()
+                    in_done.record(self.s_in)
+                with torch.cuda.stream(self.s_comp):
+                    self.s_comp.wait_event(in_done)
+                    o = paro_attention(bufs[0], bufs[1], bufs[2], self.pplans[c], self.plans[c], i_block=0, **self.kw)
+                    ev = torch.cuda.Event()
+                    ev.record(self.s_comp)
+                    comp_done.append(ev)
+                with torch.cuda.stream(self.s_out):
+                    self.s_out.wait_event(ev)
+                    o.record_stream(self.s_out)
+                    for b in range(B):
+                        out[b, h0:h1].copy_(o[b], non_blocking=True)
+                    last_out = torch.cuda.Event()
+                    last_out.record(self.s_out)
+            main.wait_event(last_out)
+            main.wait_event(comp_done[-1])
+        return out

@@ -189,3 +189,25 @@ def test_processors_on_a_stand_in_attention_module():
     qkv = [f(hs).view(1, -1, heads, D).transpose(1, 2).float() for f in (attn.to_q, attn.to_k, attn.to_v)]
     ref = attn.to_out[0](torch.nn.functional.scaled_dot_product_attention(*qkv).transpose(1, 2).reshape(1, -1, heads * D).to(torch.bfloat16))
     assert torch.nn.functional.cosine_similarity(out.float().flatten(), ref.float().flatten(), dim=0) > 0.99
+
+
+def test_host_pipelined_matches_device_call():
+    """Pinned host tensors through the head-group pipeline give bit-identical results."""
+    B, H, D, grid, n_text = 2, 6, 64, (2, 6, 10), 8
+    N = n_text + grid[0] * grid[1] * grid[2]
+    q, k, v, orders = po.make_inputs(B, H, N, D, torch.bfloat16, seed=21)
+    nb = (N + 63) // 64
+    mask = po.make_mask(H, nb, 0.6, seed=21, text_blocks=1)
+    tabs = pb.rope_tables(grid, D, "cogvideox")
+    want = pb.paro_attention(q.to(DEV), k.to(DEV), v.to(DEV), torch.tensor(orders), mask.to(DEV), grid_fhw=grid,
+                             n_text=n_text, rope=tabs)
+    pipe = pb.HostPipelinedAttention(orders, mask, (B, H, N, D), torch.bfloat16, grid_fhw=grid, n_text=n_text, rope=tabs,
+                                     heads_per_group=4)
+    hq, hk, hv = (t.pin_memory() for t in (q, k, v))
+    for _ in range(2):
+        got = pipe(hq, hk, hv)
+        torch.cuda.synchronize()
+        pb.check_status()
+        assert torch.equal(got, want.cpu())
+    with pytest.raises(ValueError):
+        pipe(q, k, v)   # not pinned
