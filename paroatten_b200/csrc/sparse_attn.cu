@@ -205,7 +205,7 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
   const uint32_t tS = tmem_base, tP = tmem_base + 64u, tQ = tmem_base + 96u, tO = tmem_base + 128u;
 
   if (warp >= 8) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 48;");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 32;");
     if (warp == 8 && lane == 0) {
       // ---------------------------------------------------------------- TMA producer: K ring
       tma_prefetch_desc(&tm_k);
@@ -305,7 +305,7 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
     }
   } else {
     // ------------------------------------------------------------------ softmax + epilogue
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 96;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 104;");
     const int qd = warp & 3;                 // TMEM lane quadrant this warp may touch
     const int ch = warp >> 2;                // which 32 score columns (and which half of O's columns)
     const int r = qd * 32 + lane;            // row inside the 128-row tile
