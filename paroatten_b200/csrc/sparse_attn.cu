@@ -157,15 +157,16 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
   uint64_t* bar_vfull = bar_qkdone + KST;               // [VST]  V tile landed
   uint64_t* bar_pvdone = bar_vfull + VST;               // [VST]  P.V of the tile in this V stage finished:
                                                         //        O up to date (softmax) and V stage free (producer)
-  uint64_t* bar_pready = bar_pvdone + VST;              // [1]    P written (softmax -> MMA issuer)
-  uint64_t* bar_sfree = bar_pready + 1;                 // [1]    scores copied to registers (softmax -> MMA issuer)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_sfree + 1);
+  uint64_t* bar_pready = bar_pvdone + VST;              // [2]    P of one half written (softmax -> P.V issuer)
+  uint64_t* bar_sfree = bar_pready + 2;                 // [2]    scores of one half copied to registers
+                                                        //        (softmax -> Q.K^T issuer)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_sfree + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* s_vscale = reinterpret_cast<float*>(aux + 512);   // [D]
   float* s_vm = s_vscale + D;                              // [D]
   float* s_xchg = reinterpret_cast<float*>(aux + 1536);    // [2 buffers][2 column halves][128 rows]
   static_assert(512 + 2 * D * 4 <= 1536 && 1536 + 2 * 2 * 128 * 4 <= Cfg::AUX_BYTES, "aux area too small");
-  static_assert((3 + 2 * KST + 2 * VST) * 8 + 8 <= 512, "barrier area too small");
+  static_assert((5 + 2 * KST + 2 * VST) * 8 + 8 <= 512, "barrier area too small");
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int bh = blockIdx.x / p.npairs, pair = blockIdx.x % p.npairs;
@@ -189,8 +190,10 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
       mbar_init(bar_vfull + i, 1);
       mbar_init(bar_pvdone + i, 1);
     }
-    mbar_init(bar_pready, ATT_SOFTMAX_THREADS / 32);
-    mbar_init(bar_sfree, ATT_SOFTMAX_THREADS / 32);
+    for (int h = 0; h < 2; ++h) {   // four warps per half arrive
+      mbar_init(bar_pready + h, ATT_SOFTMAX_THREADS / 64);
+      mbar_init(bar_sfree + h, ATT_SOFTMAX_THREADS / 64);
+    }
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -257,11 +260,12 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
         ATT_WAIT(bar_q, 0, 2, -1)
         bool ok = true;
         for (int i = 0; i < n_steps && ok; ++i) {
-          if (i > 0) { ATT_WAIT(bar_sfree, (i - 1) & 1, 10, i) }   // scores of step i-1 are in registers
           for (int h = 0; h < 2; ++h) {   // one lane-masked MMA group per half that still has blocks
             if (i >= (h ? n_b : n_a)) continue;
             const int t = seq(i, h), st = t % KST;
-            if (!mbar_wait_bounded(bar_kfull + st, (t / KST) & 1, abort_flag, WAIT_LIMIT)) {
+            // this half's scores of step i-1 are in registers, its rows of S may be overwritten
+            if ((i > 0 && !mbar_wait_bounded(bar_sfree + h, (i - 1) & 1, abort_flag, WAIT_LIMIT)) ||
+                !mbar_wait_bounded(bar_kfull + st, (t / KST) & 1, abort_flag, WAIT_LIMIT)) {
               report_timeout(p, abort_flag, 3, i);
               ok = false;
               break;
@@ -281,13 +285,11 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
       constexpr uint32_t IDESC_PV = instr_desc(1, 0, 0, 128, D);   // f32 += f16 * f16
       bool ok = true;
       for (int i = 0; i < n_steps && ok; ++i) {
-#ifndef PARO_ABL_NO_PWAIT
-        ATT_WAIT(bar_pready, i & 1, 4, i)
-#endif
         for (int h = 0; h < 2; ++h) {
           if (i >= (h ? n_b : n_a)) continue;
           const int t = seq(i, h), st = t % VST;
-          if (!mbar_wait_bounded(bar_vfull + st, (t / VST) & 1, abort_flag, WAIT_LIMIT)) {
+          if (!mbar_wait_bounded(bar_pready + h, i & 1, abort_flag, WAIT_LIMIT) ||
+              !mbar_wait_bounded(bar_vfull + st, (t / VST) & 1, abort_flag, WAIT_LIMIT)) {
             report_timeout(p, abort_flag, 5, i);
             ok = false;
             break;
@@ -352,31 +354,8 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
     int kb_next = n_mine > 0 ? my_cols[0] : 0;
     float ks_next = n_mine > 0 ? kscale_bh[kb_next] : 0.f;
     TR_DECL;
-    for (int i = 0; i < n_steps; ++i) {
+    for (int i = 0; i < n_mine; ++i) {   // the two halves only meet in the issuers' queues
       TR_MARK;
-      if (i >= n_mine) {
-        // this half has no blocks left: keep the step barriers going, but never arrive for step i
-        // before step i-1 of the P barrier has completed (an early arrival would be counted there)
-        if (i > 0) {
-          ok = __all_sync(0xffffffffu, mbar_wait_bounded(bar_pready, (i - 1) & 1, abort_flag, WAIT_LIMIT));
-          if (!ok) {
-            report_timeout(p, abort_flag, 11, i);
-            break;
-          }
-        }
-        // the last P.V of this half is awaited now, while its ring barrier is still within one
-        // phase (in the epilogue the other half's later tiles would have moved it on)
-        if (i == n_mine && n_mine > 0) {
-          ok = wait_tile(bar_pvdone, VST, seq(n_mine - 1, half), 8, i);
-          if (!ok) break;
-        }
-        __syncwarp();
-        if (lane == 0) {
-          mbar_arrive(bar_sfree);
-          mbar_arrive(bar_pready);
-        }
-        continue;
-      }
       const int kb = kb_next;
       const float kscale = ks_next;
       if (i + 1 < n_mine) {   // fetched one step ahead so that the loads are off the critical path
@@ -400,7 +379,7 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
           // the scores are in registers: let the issuer overwrite S with the next step's
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(bar_sfree);
+          if (lane == 0) mbar_arrive(bar_sfree + half);
           // int32 scores -> fp32 (exact: |s| < 2^24)
 #pragma unroll
           for (int j = 0; j < 32; ++j) f[j] = (float)(int)s[j];
@@ -486,7 +465,7 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar_pready);   // one arrival per warp
+      if (lane == 0) mbar_arrive(bar_pready + half);   // one arrival per warp
       TR_ACC(5);
     }
 #ifdef PARO_ATTN_TRACE
@@ -499,7 +478,7 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
 
     // epilogue (the TMEM loads are warp-collective: every lane of the warp executes them, rows past
     // the end of the sequence only skip the store)
-    if (ok && n_mine > 0 && n_mine == n_steps) ok = wait_tile(bar_pvdone, VST, seq(n_mine - 1, half), 8, n_mine);
+    if (ok && n_mine > 0) ok = wait_tile(bar_pvdone, VST, seq(n_mine - 1, half), 8, n_mine);
     // row sum = both threads' shares (reached by every softmax thread, also after a failed wait)
     float* xl = s_xchg;
     named_barrier(1, ATT_SOFTMAX_THREADS);
