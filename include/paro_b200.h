@@ -117,6 +117,27 @@ int paro_quant_v_fp8(const void* v, int dtype, int B, int H, int N, int D,
                      float* v_scale, float* vm, void* scratch, size_t scratch_bytes,
                      paro_stream_t stream);
 
+/* Fused pre-attention passes: the same quantisers reading the NATURAL-order activations through
+ * the RoPE + per-head reordering front end of paro_rope_permute, so that the reordered 16-bit copy
+ * is never written (the processors' sequence apply_rotary_emb -> permute_qk -> per_warp_int8,
+ * cogvideox.py:167-186, in one or two passes per tensor).  Arguments as in paro_rope_permute and
+ * paro_quant_int8 / paro_quant_v_fp8.  paro_prep_qk_int8: smooth != 0 first reduces the mean of
+ * the rotated values into km_out ([B,H,D], input dtype; needs scratch of
+ * paro_channel_stats_scratch_bytes) and subtracts it.  paro_prep_v_fp8: V is reordered only (never
+ * rotated); v8 or v16 may be NULL. */
+int paro_prep_qk_int8(const void* x, int dtype, int B, int H, int N, int D,
+                      int64_t stride_b, int64_t stride_h, int64_t stride_n,
+                      int n_text, int F, int Hh, int W, const int32_t* order_ids,
+                      int rope_mode, const void* cos_tab, const void* sin_tab, int pairs_f, int pairs_h,
+                      int group, int smooth, void* km_out, int8_t* out, float* scale,
+                      void* scratch, size_t scratch_bytes, paro_stream_t stream);
+int paro_prep_v_fp8(const void* v, int dtype, int B, int H, int N, int D,
+                    int64_t stride_b, int64_t stride_h, int64_t stride_n,
+                    int n_text, int F, int Hh, int W, const int32_t* order_ids,
+                    int smooth, float scale_max, uint8_t* v8, uint16_t* v16,
+                    float* v_scale, float* vm, void* scratch, size_t scratch_bytes,
+                    paro_stream_t stream);
+
 /* ---- sparse plan ----------------------------------------------------------------------- */
 
 /* mask: bytes [slices, nbq, nbk], non-zero = keep (the `sparse` argument of

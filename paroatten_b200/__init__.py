@@ -5,13 +5,14 @@ from .core import (check_status, paro_attention, paroattn, paroattn_qk_int8_pv_f
 from .host import HostPipelinedAttention
 from .plan import CompactPlan, PermutePlan, SparsePlan, compact_plan, perm_index
 from .processors import PARO_CogVideoXAttnProcessor2_0, PARO_WanAttnProcessor2_0, TimestepCallback
-from .quant import channel_mean, per_block_int8, per_channel_fp8, per_warp_int8, sub_mean
+from .quant import (channel_mean, per_block_int8, per_channel_fp8, per_warp_int8, prep_qk_int8, prep_v_fp8,
+                    sub_mean)
 from .rope import RopeTables, rope_permutation, rope_permute, rope_tables
 
 __all__ = [
     "paroattn", "paroattn_qk_int8_pv_fp16_cuda", "paro_attention", "sparse_attn_quantized", "check_status",
     "PARO_CogVideoXAttnProcessor2_0", "PARO_WanAttnProcessor2_0", "TimestepCallback",
-    "per_block_int8", "per_warp_int8", "sub_mean", "per_channel_fp8", "channel_mean",
+    "per_block_int8", "per_warp_int8", "sub_mean", "per_channel_fp8", "channel_mean", "prep_qk_int8", "prep_v_fp8",
     "rope_permutation", "rope_permute", "rope_tables", "RopeTables",
     "HostPipelinedAttention", "CompactPlan", "SparsePlan", "PermutePlan", "compact_plan", "perm_index",
 ]

@@ -91,6 +91,10 @@ SIGNATURES = {
     "paro_quant_int8": (_i32, [_vp, _i32, _i32, _i32, _i32, _i32, _i64, _i64, _i64, _vp, _f32, _i32, _vp, _vp, _vp]),
     "paro_quant_v_fp8": (_i32, [_vp, _i32, _i32, _i32, _i32, _i32, _i64, _i64, _i64, _i32, _f32, _vp, _vp, _vp, _vp,
                                 _vp, _sz, _vp]),
+    "paro_prep_qk_int8": (_i32, [_vp, _i32, _i32, _i32, _i32, _i32, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _vp,
+                                 _i32, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "paro_prep_v_fp8": (_i32, [_vp, _i32, _i32, _i32, _i32, _i32, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _vp,
+                               _i32, _f32, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "paro_plan_count": (_i32, [_vp, _i32, _i32, _i32, _vp, _vp, _vp]),
     "paro_plan_fill": (_i32, [_vp, _i32, _i32, _i32, _vp, _vp, _i64, _vp, _vp, _i64, _vp]),
     "paro_sparse_attn": (_i32, [_vp, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _vp, _i32, _vp, _i32,

@@ -8,7 +8,8 @@ import torch.nn.functional as F
 
 from . import _lib
 from .plan import CompactPlan, PermutePlan, SparsePlan, compact_plan, perm_index
-from .quant import _hnd, channel_mean, per_channel_fp8, per_warp_int8, per_block_int8
+from .quant import (_hnd, _quant_int8, channel_mean, per_channel_fp8, per_warp_int8, per_block_int8, prep_qk_int8,
+                    prep_v_fp8)
 from .rope import RopeTables, rope_permute
 
 _status = {}
@@ -201,12 +202,16 @@ def paro_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, permute_pl
             plan = compact_plan(sparse_plan[i_timestep, i_block].to(dev))
         else:
             plan = compact_plan(sparse_plan.to(dev))
-        qp = rope_permute(q, orders, grid, n_text, rope, tensor_layout=tensor_layout)
-        kp = rope_permute(k, orders, grid, n_text, rope, tensor_layout=tensor_layout)
-        vp = rope_permute(v, orders, grid, n_text, None, tensor_layout=tensor_layout)
-        km = channel_mean(kp) if smooth_k else None
-        q8, qs, k8, ks = per_warp_int8(qp, kp, km, BLKQ=64, WARPQ=32, BLKK=64)
-        _, vs, vm, v16 = per_channel_fp8(vp, smooth_v=smooth_v, return_f16=True)
+        # Q and V: the quantisers read the natural-order tensors through the RoPE + reordering front end
+        # (no reordered 16-bit copy).  Smoothed K needs the mean of the rotated values first; rotating
+        # twice costs more than writing the rotated copy once, so K keeps the two-step form.
+        q8, qs, _ = prep_qk_int8(q, orders, grid, n_text, rope, group=32, tensor_layout=tensor_layout)
+        if smooth_k:
+            kp = rope_permute(k, orders, grid, n_text, rope, tensor_layout=tensor_layout)
+            k8, ks = _quant_int8(kp, "HND", 64, km=channel_mean(kp))
+        else:
+            k8, ks, _ = prep_qk_int8(k, orders, grid, n_text, rope, group=64, tensor_layout=tensor_layout)
+        v16, vs, vm, _ = prep_v_fp8(v, orders, grid, n_text, smooth_v=smooth_v, tensor_layout=tensor_layout)
         res = sparse_attn_quantized(q8, qs, k8, ks, v16, vs, vm, plan, sm_scale, out_dtype=q.dtype, q_group=32,
                                     inv_index=index, n_text=n_text, return_lse=return_lse, out_layout=tensor_layout)
     o, lse = res if return_lse else (res, None)

@@ -6,8 +6,37 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "perm.cuh"
+#include "rope.cuh"
 
 namespace paro {
+
+// Optional front end of the fused kernels: row `tok` of the (reordered) sequence is read from
+// token source(tok) of the input and rotated by that token's grid position, i.e. the quantisers
+// consume RoPE + per-head reordering on the fly instead of a materialised bf16 copy.
+struct Gather {
+  int enabled;        // 0: plain input, tok -> tok, no RoPE
+  int n_text, F, Hh, W;
+  const int32_t* order_ids;   // [H] or nullptr (natural order)
+  RopeArgs rope;
+};
+
+struct GatherCtx {
+  const Gather& g;
+  PermDecoder dec;
+  __device__ GatherCtx(const Gather& g_, int h)
+      : g(g_), dec(g_.enabled && g_.order_ids ? g_.order_ids[h] : 0, g_.F, g_.Hh, g_.W) {}
+  // source token of row `tok`; f < 0 for rows that are not rotated (text tokens, or no gather)
+  __device__ __forceinline__ int source(int tok, int& f, int& y, int& x) const {
+    f = y = x = -1;
+    if (!g.enabled || tok < g.n_text) return tok;
+    const int src = g.n_text + dec.source(tok - g.n_text, f, y, x);
+    return src;
+  }
+  template <typename T> __device__ __forceinline__ void rotate(Pack8<T>& v, int c8, int D, int f, int y, int x) const {
+    if (g.enabled && g.rope.mode != PARO_ROPE_NONE && f >= 0) rotate8<T>(v, c8, D, f, y, x, g.F, g.Hh, g.rope);
+  }
+};
 
 constexpr int STATS_CHUNK = 512;  // tokens reduced by one CTA of the channel-statistics pass
 
@@ -23,7 +52,7 @@ struct ChannelPartial {
 template <typename T, int D>
 __global__ void __launch_bounds__(256)
 channel_stats_kernel(const T* __restrict__ x, int H, int N, int64_t sb, int64_t sh, int64_t sn,
-                     ChannelPartial* __restrict__ part, int chunks) {
+                     ChannelPartial* __restrict__ part, int chunks, const Gather gather) {
   constexpr int TPR = D / 8;
   constexpr int ROWS = 256 / TPR;
   __shared__ double s_sum[ROWS][D + 1];
@@ -33,13 +62,17 @@ channel_stats_kernel(const T* __restrict__ x, int H, int N, int64_t sb, int64_t 
   const int c8 = (threadIdx.x % TPR) * 8, r = threadIdx.x / TPR;
   const int t0 = blockIdx.x * STATS_CHUNK, t1 = min(N, t0 + STATS_CHUNK);
   const T* base = x + b * sb + h * sh;
+  const GatherCtx gc(gather, h);
   double sum[8];
   float mx[8], mn[8];
 #pragma unroll
   for (int j = 0; j < 8; ++j) { sum[j] = 0.0; mx[j] = -INFINITY; mn[j] = INFINITY; }
   for (int t = t0 + r; t < t1; t += ROWS) {
     Pack8<T> v;
-    v.v = *reinterpret_cast<const uint4*>(base + (size_t)t * sn + c8);
+    int gf, gy, gx;
+    const int src = gc.source(t, gf, gy, gx);
+    v.v = *reinterpret_cast<const uint4*>(base + (size_t)src * sn + c8);
+    gc.rotate(v, c8, D, gf, gy, gx);
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const float f = F16Traits<T>::to_float(v.e[j]);
@@ -98,7 +131,7 @@ template <typename T, int D, int GROUP>
 __global__ void __launch_bounds__(128)
 quant_int8_kernel(const T* __restrict__ x, const T* __restrict__ km, int8_t* __restrict__ out,
                   float* __restrict__ scale, int H, int N, int64_t sb, int64_t sh, int64_t sn,
-                  float fold, int n_scale_per_bh) {
+                  float fold, int n_scale_per_bh, const Gather gather) {
   constexpr int TPR = D / 8;          // threads per token row
   constexpr int RPL = 32 / TPR;       // rows covered by one warp-wide load
   constexpr int LOADS = 16 / RPL;     // loads per thread
@@ -108,6 +141,7 @@ quant_int8_kernel(const T* __restrict__ x, const T* __restrict__ km, int8_t* __r
   const int c8 = (lane % TPR) * 8;
   const int tok0 = blockIdx.x * 64 + warp * 16 + lane / TPR;
   const T* base = x + b * sb + h * sh;
+  const GatherCtx gc(gather, h);
 
   float mean[8];
 #pragma unroll
@@ -126,7 +160,10 @@ quant_int8_kernel(const T* __restrict__ x, const T* __restrict__ km, int8_t* __r
     const int tok = tok0 + i * RPL;
     if (tok < N) {
       Pack8<T> p;
-      p.v = *reinterpret_cast<const uint4*>(base + (size_t)tok * sn + c8);
+      int gf, gy, gx;
+      const int src = gc.source(tok, gf, gy, gx);
+      p.v = *reinterpret_cast<const uint4*>(base + (size_t)src * sn + c8);
+      gc.rotate(p, c8, D, gf, gy, gx);
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         float f = F16Traits<T>::to_float(p.e[j]);
@@ -187,7 +224,7 @@ template <typename T, int D>
 __global__ void __launch_bounds__(256)
 quant_v_fp8_kernel(const T* __restrict__ v, int H, int N, int npad, int64_t sb, int64_t sh, int64_t sn,
                    const float* __restrict__ inv_tab, const float* __restrict__ mean_tab,
-                   uint8_t* __restrict__ v8, __half* __restrict__ v16) {
+                   uint8_t* __restrict__ v8, __half* __restrict__ v16, const Gather gather) {
   constexpr int TPR = D / 8;
   constexpr int ROWS = 256 / TPR;
   constexpr int LD = D + 8;                 // padded row, keeps 16-byte alignment
@@ -197,11 +234,13 @@ quant_v_fp8_kernel(const T* __restrict__ v, int H, int N, int npad, int64_t sb, 
   const int t0 = blockIdx.x * 64;
   const T* base = v + b * sb + h * sh;
   {
+    const GatherCtx gc(gather, h);
     const int c8 = (threadIdx.x % TPR) * 8;
 #pragma unroll
     for (int r = threadIdx.x / TPR; r < 64; r += ROWS) {
       uint4 val = make_uint4(0, 0, 0, 0);
-      if (t0 + r < N) val = *reinterpret_cast<const uint4*>(base + (size_t)(t0 + r) * sn + c8);
+      int gf, gy, gx;
+      if (t0 + r < N) val = *reinterpret_cast<const uint4*>(base + (size_t)gc.source(t0 + r, gf, gy, gx) * sn + c8);
       *reinterpret_cast<uint4*>(&tile[r * LD + c8]) = val;
     }
   }
@@ -229,7 +268,7 @@ quant_v_fp8_kernel(const T* __restrict__ v, int H, int N, int npad, int64_t sb, 
   const size_t o = ((size_t)bh * D + d) * npad + t0 + run * RUN;
 #pragma unroll
   for (int i = 0; i < RUN / 16; ++i)
-    *reinterpret_cast<uint4*>(v8 + o + i * 16) = make_uint4(w8[4 * i], w8[4 * i + 1], w8[4 * i + 2], w8[4 * i + 3]);
+    if (v8) *reinterpret_cast<uint4*>(v8 + o + i * 16) = make_uint4(w8[4 * i], w8[4 * i + 1], w8[4 * i + 2], w8[4 * i + 3]);
   if (v16) {
 #pragma unroll
     for (int i = 0; i < RUN / 8; ++i)
@@ -253,12 +292,12 @@ size_t stats_bytes(int B, int H, int N, int D) {
 
 template <typename T>
 void launch_stats(const void* x, int B, int H, int N, int D, int64_t sb, int64_t sh, int64_t sn,
-                  ChannelPartial* part, cudaStream_t s) {
+                  ChannelPartial* part, cudaStream_t s, const Gather& g = Gather{}) {
   dim3 grid(stats_chunks(N), B * H);
   if (D == 128)
-    channel_stats_kernel<T, 128><<<grid, 256, 0, s>>>((const T*)x, H, N, sb, sh, sn, part, stats_chunks(N));
+    channel_stats_kernel<T, 128><<<grid, 256, 0, s>>>((const T*)x, H, N, sb, sh, sn, part, stats_chunks(N), g);
   else
-    channel_stats_kernel<T, 64><<<grid, 256, 0, s>>>((const T*)x, H, N, sb, sh, sn, part, stats_chunks(N));
+    channel_stats_kernel<T, 64><<<grid, 256, 0, s>>>((const T*)x, H, N, sb, sh, sn, part, stats_chunks(N), g);
 }
 
 }  // namespace
@@ -295,14 +334,14 @@ extern "C" int paro_channel_mean(const void* x, int dtype, int B, int H, int N, 
 namespace {
 template <typename T, int D>
 int launch_int8(const void* x, const void* km, int8_t* out, float* scale, int B, int H, int N, int64_t sb,
-                int64_t sh, int64_t sn, float fold, int group, cudaStream_t s) {
+                int64_t sh, int64_t sn, float fold, int group, cudaStream_t s, const Gather& g = Gather{}) {
   const int nb = (N + 63) / 64;
   dim3 grid(nb, B * H);
   if (group == 64)
-    quant_int8_kernel<T, D, 64><<<grid, 128, 0, s>>>((const T*)x, (const T*)km, out, scale, H, N, sb, sh, sn, fold, nb);
+    quant_int8_kernel<T, D, 64><<<grid, 128, 0, s>>>((const T*)x, (const T*)km, out, scale, H, N, sb, sh, sn, fold, nb, g);
   else
     quant_int8_kernel<T, D, 32><<<grid, 128, 0, s>>>((const T*)x, (const T*)km, out, scale, H, N, sb, sh, sn, fold,
-                                                     nb * 2);
+                                                     nb * 2, g);
   return check_launch("quant_int8_kernel");
 }
 }  // namespace
@@ -327,23 +366,23 @@ namespace {
 template <typename T>
 int run_v_fp8(const void* v, int B, int H, int N, int D, int64_t sb, int64_t sh, int64_t sn, int smooth,
               float scale_max, uint8_t* v8, uint16_t* v16, float* v_scale, float* vm, void* scratch,
-              cudaStream_t s) {
+              cudaStream_t s, const Gather& g = Gather{}) {
   const int chunks = stats_chunks(N);
   const size_t bh = (size_t)B * H;
   ChannelPartial* part = static_cast<ChannelPartial*>(scratch);
   float* inv_tab = reinterpret_cast<float*>(part + bh * chunks * D);
   float* mean_tab = inv_tab + bh * D;
-  launch_stats<T>(v, B, H, N, D, sb, sh, sn, part, s);
+  launch_stats<T>(v, B, H, N, D, sb, sh, sn, part, s);   // statistics do not depend on the token order
   channel_finalize_kernel<T><<<B * H, D, 0, s>>>(part, chunks, D, N, smooth, scale_max, (T*)nullptr,
                                                  smooth ? vm : nullptr, v_scale, inv_tab, mean_tab);
   const int npad = (N + 63) / 64 * 64;
   dim3 grid(npad / 64, B * H);
   if (D == 128)
     quant_v_fp8_kernel<T, 128><<<grid, 256, 0, s>>>((const T*)v, H, N, npad, sb, sh, sn, inv_tab, mean_tab, v8,
-                                                    (__half*)v16);
+                                                    (__half*)v16, g);
   else
     quant_v_fp8_kernel<T, 64><<<grid, 256, 0, s>>>((const T*)v, H, N, npad, sb, sh, sn, inv_tab, mean_tab, v8,
-                                                   (__half*)v16);
+                                                   (__half*)v16, g);
   return check_launch("quant_v_fp8", 3);
 }
 }  // namespace
@@ -432,4 +471,98 @@ extern "C" int paro_channel_mean_noalloc(const void* x, int dtype, int B, int H,
                                                                nullptr);
   }
   return check_launch("channel_mean_noalloc", 2);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Fused pre-attention entry points: the quantisers read the natural-order activations through the
+// RoPE + reordering front end, so no reordered 16-bit copy of Q, K, V is ever written to HBM.
+namespace {
+
+int make_gather(Gather* g, const char* who, int N, int D, int n_text, int F, int Hh, int W, const int32_t* order_ids,
+                int rope_mode, const void* cos_tab, const void* sin_tab, int pairs_f, int pairs_h) {
+  PARO_REQUIRE(F > 0 && Hh > 0 && W > 0 && n_text >= 0 && (int64_t)n_text + (int64_t)F * Hh * W == N, PARO_ESHAPE,
+               "%s: n_text + F*H*W = %lld != N = %d", who, (long long)n_text + (long long)F * Hh * W, N);
+  PARO_REQUIRE(rope_mode >= PARO_ROPE_NONE && rope_mode <= PARO_ROPE_COMPLEX_F64, PARO_EINVAL,
+               "%s: unknown rope_mode %d", who, rope_mode);
+  if (rope_mode != PARO_ROPE_NONE) {
+    PARO_REQUIRE(cos_tab && sin_tab, PARO_EINVAL, "%s: rope tables missing", who);
+    PARO_REQUIRE(pairs_f >= 0 && pairs_h >= 0 && pairs_f + pairs_h <= D / 2, PARO_ESHAPE,
+                 "%s: pairs_f + pairs_h exceeds D/2", who);
+  }
+  g->enabled = 1;
+  g->n_text = n_text; g->F = F; g->Hh = Hh; g->W = W;
+  g->order_ids = order_ids;
+  g->rope = RopeArgs{rope_mode, cos_tab, sin_tab, pairs_f, pairs_h};
+  return PARO_OK;
+}
+
+template <typename T>
+int run_prep_int8(const void* x, int B, int H, int N, int D, int64_t sb, int64_t sh, int64_t sn, const Gather& g,
+                  int group, int smooth, void* km_out, int8_t* out, float* scale, void* scratch, cudaStream_t s) {
+  const T* km = nullptr;
+  int launches = 1;
+  if (smooth) {
+    // mean of the rotated values; the token order does not matter for it, so the statistics pass
+    // reads the input in natural order (rotation only)
+    Gather gs = g;
+    gs.order_ids = nullptr;
+    ChannelPartial* part = static_cast<ChannelPartial*>(scratch);
+    launch_stats<T>(x, B, H, N, D, sb, sh, sn, part, s, gs);
+    channel_finalize_kernel<T><<<B * H, D, 0, s>>>(part, stats_chunks(N), D, N, 1, 1.f, (T*)km_out, nullptr, nullptr,
+                                                   nullptr, nullptr);
+    km = static_cast<const T*>(km_out);
+    launches = 3;
+  }
+  int rc = D == 128 ? launch_int8<T, 128>(x, km, out, scale, B, H, N, sb, sh, sn, 0.f, group, s, g)
+                    : launch_int8<T, 64>(x, km, out, scale, B, H, N, sb, sh, sn, 0.f, group, s, g);
+  if (rc == PARO_OK) count_launches(launches - 1);
+  return rc;
+}
+
+}  // namespace
+
+extern "C" int paro_prep_qk_int8(const void* x, int dtype, int B, int H, int N, int D,
+                                 int64_t stride_b, int64_t stride_h, int64_t stride_n,
+                                 int n_text, int F, int Hh, int W, const int32_t* order_ids,
+                                 int rope_mode, const void* cos_tab, const void* sin_tab, int pairs_f, int pairs_h,
+                                 int group, int smooth, void* km_out, int8_t* out, float* scale,
+                                 void* scratch, size_t scratch_bytes, paro_stream_t stream) {
+  if (int rc = check_tensor("paro_prep_qk_int8(x)", x, dtype, B, H, N, D, stride_b, stride_h, stride_n)) return rc;
+  PARO_REQUIRE(group == 32 || group == 64, PARO_EINVAL, "paro_prep_qk_int8: group must be 32 or 64, got %d", group);
+  PARO_REQUIRE(out && scale && aligned16(out), PARO_EINVAL, "paro_prep_qk_int8: null or unaligned output");
+  Gather g{};
+  if (int rc = make_gather(&g, "paro_prep_qk_int8", N, D, n_text, F, Hh, W, order_ids, rope_mode, cos_tab, sin_tab,
+                           pairs_f, pairs_h))
+    return rc;
+  if (smooth) {
+    PARO_REQUIRE(km_out && aligned16(km_out), PARO_EINVAL, "paro_prep_qk_int8: smoothing needs the km output");
+    PARO_REQUIRE(scratch && aligned16(scratch) && scratch_bytes >= stats_bytes(B, H, N, D), PARO_ECAP,
+                 "paro_prep_qk_int8: scratch too small (%zu < %zu)", scratch_bytes, stats_bytes(B, H, N, D));
+  }
+  cudaStream_t s = (cudaStream_t)stream;
+  return dtype == PARO_F16
+             ? run_prep_int8<__half>(x, B, H, N, D, stride_b, stride_h, stride_n, g, group, smooth, km_out, out, scale, scratch, s)
+             : run_prep_int8<__nv_bfloat16>(x, B, H, N, D, stride_b, stride_h, stride_n, g, group, smooth, km_out, out, scale, scratch, s);
+}
+
+extern "C" int paro_prep_v_fp8(const void* v, int dtype, int B, int H, int N, int D,
+                               int64_t stride_b, int64_t stride_h, int64_t stride_n,
+                               int n_text, int F, int Hh, int W, const int32_t* order_ids,
+                               int smooth, float scale_max, uint8_t* v8, uint16_t* v16,
+                               float* v_scale, float* vm, void* scratch, size_t scratch_bytes,
+                               paro_stream_t stream) {
+  if (int rc = check_tensor("paro_prep_v_fp8(v)", v, dtype, B, H, N, D, stride_b, stride_h, stride_n)) return rc;
+  PARO_REQUIRE((v8 || v16) && v_scale, PARO_EINVAL, "paro_prep_v_fp8: null output");
+  PARO_REQUIRE(!smooth || vm, PARO_EINVAL, "paro_prep_v_fp8: smoothing needs the vm output");
+  PARO_REQUIRE(scale_max > 0.f && scale_max <= 448.f, PARO_EINVAL, "paro_prep_v_fp8: scale_max must be in (0, 448]");
+  PARO_REQUIRE((!v8 || aligned16(v8)) && (!v16 || aligned16(v16)), PARO_EALIGN, "paro_prep_v_fp8: outputs not 16-byte aligned");
+  PARO_REQUIRE(scratch && aligned16(scratch) && scratch_bytes >= stats_bytes(B, H, N, D), PARO_ECAP,
+               "paro_prep_v_fp8: scratch too small (%zu < %zu)", scratch_bytes, stats_bytes(B, H, N, D));
+  Gather g{};
+  if (int rc = make_gather(&g, "paro_prep_v_fp8", N, D, n_text, F, Hh, W, order_ids, PARO_ROPE_NONE, nullptr, nullptr, 0, 0))
+    return rc;
+  cudaStream_t s = (cudaStream_t)stream;
+  return dtype == PARO_F16
+             ? run_v_fp8<__half>(v, B, H, N, D, stride_b, stride_h, stride_n, smooth, scale_max, v8, v16, v_scale, vm, scratch, s, g)
+             : run_v_fp8<__nv_bfloat16>(v, B, H, N, D, stride_b, stride_h, stride_n, smooth, scale_max, v8, v16, v_scale, vm, scratch, s, g);
 }

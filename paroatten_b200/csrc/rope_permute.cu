@@ -3,49 +3,9 @@
 // are a few KB and stay in L1/L2.
 #include "common.cuh"
 #include "perm.cuh"
+#include "rope.cuh"
 
 namespace paro {
-
-struct RopeArgs {
-  int mode;            // PARO_ROPE_*
-  const void* cos_tab; // [F+Hh+W, D/2]
-  const void* sin_tab;
-  int pairs_f, pairs_h;
-};
-
-// Rotates the four channel pairs held in `x` (channels c8..c8+7 of a token at grid
-// coordinate f,y,x).  Products and sums are rounded separately (no fused multiply-add) so that
-// results equal a plain elementwise evaluation.
-template <typename T>
-__device__ __forceinline__ void rotate8(Pack8<T>& x, int c8, int D, int f, int y, int xw,
-                                        int F, int Hh, const RopeArgs& r) {
-  const int half = D >> 1;
-#pragma unroll
-  for (int p = 0; p < 4; ++p) {
-    const int pair = (c8 >> 1) + p;
-    const int row = pair < r.pairs_f ? f : (pair < r.pairs_f + r.pairs_h ? F + y : F + Hh + xw);
-    const size_t t = (size_t)row * half + pair;
-    if (r.mode == PARO_ROPE_REAL_F32) {
-      const float c = static_cast<const float*>(r.cos_tab)[t];
-      const float s = static_cast<const float*>(r.sin_tab)[t];
-      const float x0 = F16Traits<T>::to_float(x.e[2 * p]);
-      const float x1 = F16Traits<T>::to_float(x.e[2 * p + 1]);
-      const float o0 = __fadd_rn(__fmul_rn(x0, c), __fmul_rn(-x1, s));
-      const float o1 = __fadd_rn(__fmul_rn(x1, c), __fmul_rn(x0, s));
-      x.e[2 * p] = F16Traits<T>::from_float(o0);
-      x.e[2 * p + 1] = F16Traits<T>::from_float(o1);
-    } else {
-      const double c = static_cast<const double*>(r.cos_tab)[t];
-      const double s = static_cast<const double*>(r.sin_tab)[t];
-      const double x0 = (double)F16Traits<T>::to_float(x.e[2 * p]);
-      const double x1 = (double)F16Traits<T>::to_float(x.e[2 * p + 1]);
-      const double re = __dsub_rn(__dmul_rn(x0, c), __dmul_rn(x1, s));
-      const double im = __dadd_rn(__dmul_rn(x0, s), __dmul_rn(x1, c));
-      x.e[2 * p] = F16Traits<T>::from_float(__double2float_rn(re));
-      x.e[2 * p + 1] = F16Traits<T>::from_float(__double2float_rn(im));
-    }
-  }
-}
 
 // Block = 256 threads; a thread owns one 16-byte slice of a row and walks ROWS_PER_THREAD rows.
 // blockIdx.x: group of rows, blockIdx.y: b*H + h.

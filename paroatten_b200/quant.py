@@ -125,3 +125,56 @@ def per_channel_fp8(v: torch.Tensor, tensor_layout: str = "HND", scale_max: floa
     if tensor_layout == "NHD":
         v8 = v8.transpose(1, 2)  # [B,D,H,Npad] view, the reference's NHD output shape
     return (v8, scale, vm, v16) if return_f16 else (v8, scale, vm)
+
+
+def prep_qk_int8(x: torch.Tensor, order_ids: Optional[torch.Tensor], grid, n_text: int = 0, rope=None, group: int = 32,
+                 smooth: bool = False, tensor_layout: str = "HND"):
+    """RoPE + per-head reordering + INT8 quantisation of Q (group=32) or K (group=64, smooth=True for
+    mean smoothing) straight from the natural-order tensor: no reordered 16-bit copy is written.
+    Returns (int8 [B,H,N,D], scale, km or None), equal bit for bit to
+    per_warp_int8(rope_permute(x, ...))."""
+    _lib.require_cuda(x, order_ids)
+    xv = _hnd(x, tensor_layout)
+    B, H, N, D = xv.shape
+    nb = (N + 63) // 64
+    F, Hh, W = (int(g) for g in grid)
+    with torch.cuda.device(x.device):
+        if order_ids is not None:
+            order_ids = order_ids.to(device=x.device, dtype=torch.int32).contiguous()
+        out = torch.empty(B, H, N, D, dtype=torch.int8, device=x.device)
+        scale = torch.empty(B, H, nb * (64 // group), dtype=torch.float32, device=x.device)
+        km = torch.empty(B, H, D, dtype=x.dtype, device=x.device) if smooth else None
+        scr = _stats_scratch(B, H, N, D, x.device) if smooth else None
+        r = rope
+        _lib.check(_lib.lib().paro_prep_qk_int8(
+            xv.data_ptr(), _lib.dtype_code(x.dtype), B, H, N, D, xv.stride(0), xv.stride(1), xv.stride(2),
+            int(n_text), F, Hh, W, _lib.ptr(order_ids), r.mode if r is not None else _lib.ROPE_NONE,
+            _lib.ptr(r.cos if r else None), _lib.ptr(r.sin if r else None), r.pairs_f if r else 0,
+            r.pairs_h if r else 0, int(group), int(bool(smooth)), _lib.ptr(km), out.data_ptr(), scale.data_ptr(),
+            _lib.ptr(scr), scr.numel() if scr is not None else 0, _lib.stream_ptr()))
+    return out, scale, km
+
+
+def prep_v_fp8(v: torch.Tensor, order_ids: Optional[torch.Tensor], grid, n_text: int = 0, smooth_v: bool = True,
+               scale_max: float = 448.0, tensor_layout: str = "HND", want_fp8: bool = False):
+    """Per-head reordering + per-channel FP8 quantisation of V from the natural-order tensor.
+    Returns (v_f16 [B,H,D,ceil64(N)] holding the e4m3 values, v_scale, vm, v_fp8 or None), equal
+    bit for bit to per_channel_fp8(rope_permute(v, ...), return_f16=True)."""
+    _lib.require_cuda(v, order_ids)
+    vv = _hnd(v, tensor_layout)
+    B, H, N, D = vv.shape
+    npad = (N + 63) // 64 * 64
+    F, Hh, W = (int(g) for g in grid)
+    with torch.cuda.device(v.device):
+        if order_ids is not None:
+            order_ids = order_ids.to(device=v.device, dtype=torch.int32).contiguous()
+        v16 = torch.empty(B, H, D, npad, dtype=torch.float16, device=v.device)
+        v8 = torch.empty(B, H, D, npad, dtype=torch.float8_e4m3fn, device=v.device) if want_fp8 else None
+        scale = torch.empty(B, H, D, dtype=torch.float32, device=v.device)
+        vm = torch.empty(B, H, D, dtype=torch.float32, device=v.device) if smooth_v else None
+        scr = _stats_scratch(B, H, N, D, v.device)
+        _lib.check(_lib.lib().paro_prep_v_fp8(
+            vv.data_ptr(), _lib.dtype_code(v.dtype), B, H, N, D, vv.stride(0), vv.stride(1), vv.stride(2),
+            int(n_text), F, Hh, W, _lib.ptr(order_ids), int(bool(smooth_v)), float(scale_max), _lib.ptr(v8),
+            v16.data_ptr(), scale.data_ptr(), _lib.ptr(vm), scr.data_ptr(), scr.numel(), _lib.stream_ptr()))
+    return v16, scale, vm, v8

@@ -160,3 +160,36 @@ def test_argument_errors():
     z = torch.zeros(1, 2, 50, 64, dtype=torch.float16, device=DEV)
     with pytest.raises(ValueError, match="!= N"):
         pb.rope_permute(z, None, (1, 7, 7))
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("D,family,grid,n_text", [(64, "cogvideox", (3, 6, 10), 17), (128, "wan", (2, 5, 9), 0),
+                                                  (128, "wan", (3, 7, 11), 40)])
+def test_fused_prep_equals_separate_passes(dtype, D, family, grid, n_text):
+    """RoPE + reorder + quantise in one pass gives the very same bytes as the separate kernels and
+    as the oracle."""
+    B, H = 2, 6
+    N = n_text + grid[0] * grid[1] * grid[2]
+    q, k, v = rand((B, H, N, D), dtype, 31), rand((B, H, N, D), dtype, 32, offset=1.0), rand((B, H, N, D), dtype, 33)
+    orders = [(h * 5 + 2) % 6 for h in range(H)]
+    ids = torch.tensor(orders, dtype=torch.int32, device=DEV)
+    tabs = pb.rope_tables(grid, D, family)
+    cos, sin = po.rope_full_tables(grid, D, family)
+    fn = po.apply_rope_real if family == "cogvideox" else po.apply_rope_complex
+    qp = po.permute_tokens(fn(q, cos, sin, n_text), orders, grid, n_text)
+    kp = po.permute_tokens(fn(k, cos, sin, n_text), orders, grid, n_text)
+    vp = po.permute_tokens(v, orders, grid, n_text)
+    km = po.channel_mean(kp, dtype)
+    wq, wqs = po.quant_int8(qp, 32)
+    wk, wks = po.quant_int8(kp, 64, km=km)
+    w8, wvs, wvm = po.quant_v_fp8(vp)
+    q8, qs, none = pb.prep_qk_int8(q.to(DEV), ids, grid, n_text, tabs, group=32)
+    assert none is None and torch.equal(q8.cpu(), wq) and torch.equal(qs.cpu(), wqs)
+    k8, ks, gkm = pb.prep_qk_int8(k.to(DEV), ids, grid, n_text, tabs, group=64, smooth=True)
+    assert torch.equal(gkm.cpu(), km) and torch.equal(k8.cpu(), wk) and torch.equal(ks.cpu(), wks)
+    v16, vs, vm, v8 = pb.prep_v_fp8(v.to(DEV), ids, grid, n_text, want_fp8=True)
+    assert torch.equal(v8.cpu().view(torch.uint8), w8.view(torch.uint8)) and torch.equal(v16.cpu(), w8.to(torch.float16))
+    assert torch.equal(vs.cpu(), wvs) and torch.equal(vm.cpu(), wvm)
+    # NHD input, no fp8 copy
+    v16b, _, _, none8 = pb.prep_v_fp8(v.transpose(1, 2).contiguous().to(DEV), ids, grid, n_text, tensor_layout="NHD")
+    assert none8 is None and torch.equal(v16b, v16)
