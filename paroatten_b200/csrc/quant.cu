@@ -198,17 +198,17 @@ quant_int8_kernel(const T* __restrict__ x, const T* __restrict__ km, int8_t* __r
   for (int i = 0; i < LOADS; ++i) {
     const int tok = tok0 + i * RPL;
     if (tok < N) {
+      // round to nearest even (NaN -> 0), then saturate and pack two values per instruction
+      int qi[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) qi[j] = __float2int_rn(__fmul_rn(v[i][j], inv));
       uint32_t w[2];
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
-        uint32_t acc = 0;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          int q = __float2int_rn(__fmul_rn(v[i][half * 4 + j], inv));
-          q = max(-128, min(127, q));
-          acc |= (uint32_t)(q & 0xff) << (8 * j);
-        }
-        w[half] = acc;
+        uint32_t hi16, word;
+        asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi16) : "r"(qi[half * 4 + 3]), "r"(qi[half * 4 + 2]), "r"(0));
+        asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(word) : "r"(qi[half * 4 + 1]), "r"(qi[half * 4 + 0]), "r"(hi16));
+        w[half] = word;
       }
       *reinterpret_cast<uint2*>(out + ((size_t)bh * N + tok) * D + c8) = make_uint2(w[0], w[1]);
     }
