@@ -7,7 +7,7 @@ import torch
 import torch.nn.functional as F
 
 from . import _lib
-from .plan import CompactPlan, PermutePlan, SparsePlan, compact_plan, perm_index
+from .plan import CompactPlan, PermutePlan, PlanStore, SparsePlan, compact_plan, perm_index
 from .quant import (_hnd, _quant_int8, channel_mean, per_channel_fp8, per_warp_int8, per_block_int8, prep_qk_int8,
                     prep_v_fp8)
 from .rope import RopeTables, rope_permute
@@ -194,7 +194,7 @@ def paro_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, permute_pl
             ids = permute_plan["permute"][i_block] if isinstance(permute_plan, dict) else permute_plan
             orders = torch.as_tensor(ids).to(dev, torch.int32).contiguous()
             index = perm_index(orders, grid, dev)
-        if isinstance(sparse_plan, SparsePlan):
+        if isinstance(sparse_plan, (SparsePlan, PlanStore)):
             plan = sparse_plan.get(i_timestep, i_block)
         elif isinstance(sparse_plan, CompactPlan):
             plan = sparse_plan

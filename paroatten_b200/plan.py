@@ -40,8 +40,8 @@ class CompactPlan:
     nbk: int
     row_ptr: torch.Tensor    # int32 [slices*nbq + 1]
     cols: torch.Tensor       # int32 [kept]: ascending k-block ids per q-block
-    pair_ptr: torch.Tensor   # int32 [slices*ceil(nbq/2) + 1]
-    pair_ent: torch.Tensor   # int32: kb*4 + flags per pair of adjacent q-blocks (merged walk; auxiliary)
+    pair_ptr: Optional[torch.Tensor]   # int32 [slices*ceil(nbq/2) + 1]
+    pair_ent: Optional[torch.Tensor]   # int32: kb*4 + flags per pair of adjacent q-blocks (merged walk; auxiliary)
     kept_blocks: int         # number of true entries of the mask
     pair_tiles: int          # size of the merged (union) walk over all q-block pairs
 
@@ -110,3 +110,85 @@ class PermutePlan:
         if i_block not in self._index:
             self._index[i_block] = perm_index(self.orders(i_block), self.grid, self.device)
         return self._index[i_block]
+
+
+class PlanStore:
+    """Every (timestep bin, layer) slice of a sparse plan `[T, L, H, nb, nb]`, compacted ONCE and kept
+    as walk lists in pinned host memory; the lists of the layer that runs next are streamed to the
+    GPU on a side stream while the current layer computes.
+
+    Replaces the reference's `SparseMaskPrefetchStream` (paroattention/prefetch_utils.py:34-59), which
+    double-buffers the boolean mask itself (nb*nb bytes per head and layer: 55.9 MB at Wan-14B-720p);
+    the compacted lists are 4 bytes per KEPT block (9 MB at density 0.2).  `get` has the call shape of
+    `SparsePlan.get`, so a processor can use either."""
+
+    def __init__(self, sparse: Optional[torch.Tensor] = None, device=None, _lists=None):
+        self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+        if _lists is not None:
+            self.meta, self.lists = _lists
+        else:
+            if sparse.dim() != 5:
+                raise ValueError("sparse plan must be [timestep_bins, layers, heads, nb, nb]")
+            T, L, H, nbq, nbk = (int(x) for x in sparse.shape)
+            self.meta = dict(T=T, L=L, H=H, nbq=nbq, nbk=nbk)
+            self.lists = {}
+            for t in range(T):
+                for l in range(L):
+                    p = compact_plan(sparse[t, l].to(self.device))
+                    self.lists[(t, l)] = (p.row_ptr.cpu().pin_memory(), p.cols.cpu().pin_memory())
+        cap = max(c.numel() for _, c in self.lists.values())
+        rows = self.meta["H"] * self.meta["nbq"] + 1
+        with torch.cuda.device(self.device):
+            self._buf = [(torch.empty(rows, dtype=torch.int32, device=self.device),
+                          torch.empty(max(cap, 1), dtype=torch.int32, device=self.device)) for _ in range(2)]
+            self._stream = torch.cuda.Stream(self.device)
+        self._slot = {}          # key -> (buffer index, event of its copy)
+        self._next = 0
+
+    def keys(self):
+        return sorted(self.lists)
+
+    def prefetch(self, i_timestep: int, i_block: int) -> None:
+        """Starts the host-to-device copy of one slice's lists into the buffer that `get` did not
+        hand out last.  The copy waits for everything enqueued so far on the current stream (the
+        kernels that may still read that buffer) and overlaps with whatever is enqueued afterwards."""
+        key = (int(i_timestep), int(i_block))
+        if key in self._slot or key not in self.lists:
+            return
+        b = self._next
+        self._next ^= 1
+        self._slot = {k: v for k, v in self._slot.items() if v[0] != b}
+        row_ptr, cols = self.lists[key]
+        with torch.cuda.device(self.device):
+            fence = torch.cuda.Event()
+            fence.record(torch.cuda.current_stream())
+            self._stream.wait_event(fence)
+            with torch.cuda.stream(self._stream):
+                self._buf[b][0].copy_(row_ptr, non_blocking=True)
+                self._buf[b][1][:cols.numel()].copy_(cols, non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(self._stream)
+        self._slot[key] = (b, ev)
+
+    def get(self, i_timestep: int, i_block: int) -> CompactPlan:
+        """The slice's plan, usable on the current stream (waits for its copy if one is in flight).
+        It stays valid until the second `prefetch` after this call."""
+        key = (int(i_timestep), int(i_block))
+        if key not in self._slot:
+            self.prefetch(*key)
+        b, ev = self._slot[key]
+        self._next = b ^ 1       # the next prefetch goes to the other buffer
+        n = self.lists[key][1].numel()
+        with torch.cuda.device(self.device):
+            torch.cuda.current_stream().wait_event(ev)
+        m = self.meta
+        return CompactPlan(m["H"], m["nbq"], m["nbk"], self._buf[b][0], self._buf[b][1][:n], None, None, int(n), 0)
+
+    def save(self, path: str) -> None:
+        torch.save({"meta": self.meta, "lists": {f"{t},{l}": (r.clone(), c.clone()) for (t, l), (r, c) in self.lists.items()}}, path)
+
+    @classmethod
+    def load(cls, path: str, device=None) -> "PlanStore":
+        blob = torch.load(path, map_location="cpu")
+        lists = {tuple(int(x) for x in k.split(",")): (r.pin_memory(), c.pin_memory()) for k, (r, c) in blob["lists"].items()}
+        return cls(device=device, _lists=(blob["meta"], lists))

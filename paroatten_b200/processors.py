@@ -4,7 +4,7 @@ contract (paroattention/cogvideox.py:112-250, paroattention/wan.py:113-327).
 State injected by the pipeline set-up, exactly as the reference's `paroattn_convert` does
 (example/pipeline_cogvideox.py:120-136):
     permute_plan  dict {'permute': [L,H] order ids, ...} (or a plan.PermutePlan)
-    sparse_mask   bool [T, L, H, nb, nb] (or a plan.SparsePlan)
+    sparse_mask   bool [T, L, H, nb, nb] (or a plan.SparsePlan / plan.PlanStore shared by all layers)
     i_block       layer index, i_timestep  timestep bin (set by TimestepCallback)
     grid_fhw      latent grid (F, H, W); defaults to the reference's hard-coded 13x30x45 / 21x45x80
 The processors only need `attn` to expose to_q/to_k/to_v/to_out, norm_q/norm_k and heads, so
@@ -19,7 +19,7 @@ import torch
 
 from . import _lib
 from .core import paro_attention
-from .plan import PermutePlan, SparsePlan
+from .plan import PermutePlan, PlanStore, SparsePlan
 from .rope import RopeTables, rope_tables
 
 
@@ -52,7 +52,7 @@ class _ProcessorBase:
             raise RuntimeError("processor has no sparse_mask")
         if self._splan is None or self._splan_src is not src:
             self._splan_src = src
-            self._splan = src if isinstance(src, SparsePlan) else SparsePlan(src, device)
+            self._splan = src if isinstance(src, (SparsePlan, PlanStore)) else SparsePlan(src, device)
         return self._pplan, self._splan
 
     def _rope(self, head_dim, device) -> RopeTables:
@@ -74,6 +74,8 @@ class _ProcessorBase:
                              grid_fhw=self.grid_fhw, n_text=n_text,
                              rope=self._rope(D, query.device) if use_rope else None,
                              tensor_layout="NHD", smooth_k=self.smooth_k)
+        if isinstance(splan, PlanStore):     # stream the next layer's lists in while this layer computes
+            splan.prefetch(self.i_timestep, self.i_block + 1)
         end.record()
         self._pending.append((start, end))   # read lazily: no device sync per layer
         self.call_count += 1
