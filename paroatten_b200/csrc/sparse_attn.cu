@@ -7,12 +7,14 @@
 // keeps it from writing the other half's accumulator rows, so both halves always have work (all
 // four SM sub-partitions run exponentials) and nothing is computed for blocks that are not kept.
 //
-//   warps 0-7   softmax + epilogue.  Row r of the tile is shared by two threads: warp w (< 4)
-//               takes score columns 0-31, warp w+4 columns 32-63 (both may touch TMEM lane
-//               quadrant w).  Online softmax in fp32 (base 2, lazy rescaling); the two threads
-//               exchange their partial row maximum through shared memory.  P is written to TMEM as
-//               fp16; the epilogue stores O/l * v_scale + vm at the row's un-permuted position.
-//               These warps take the registers the others give up.
+//   warps 0-7   softmax + epilogue.  Row r of the tile belongs to two threads, one in each WARP SET:
+//               warp w (< 4, set 0) handles the even steps of its half, warp w+4 (set 1) the odd
+//               steps (both may touch TMEM lane quadrant w).  A thread handles the whole row (64
+//               scores) of its steps, so two consecutive steps of a half are in flight at once.
+//               Online softmax in fp32 (base 2, lazy rescaling): the running row maximum passes
+//               from step to step through shared memory, each thread keeps its own share of the
+//               row sum.  P is written to TMEM as fp16; the epilogue stores O/l * v_scale + vm at
+//               the row's un-permuted position.  These warps take the registers the others give up.
 //   warp 8      TMA producer for the K ring (int8 tiles, freed when their Q.K^T is done)
 //   warp 9      TMA producer for the V^T ring (fp16 tiles, freed when their P.V is done)
 //   warp 10     owns TMEM; one lane issues S = Q.K^T (kind::i8, A = Q from TMEM, int32 accumulators)
@@ -21,8 +23,9 @@
 // TMEM (256 columns per CTA): S [0,64) int32 scores, P [64,96) fp16 probabilities, Q [96,128) the
 // int8 query tile (A operand of Q.K^T read from TMEM, so it is not re-read from shared memory for
 // every k-block), O [128,128+D) fp32.  The softmax threads release S as soon as they hold the scores
-// in registers, so Q.K^T of step i+1 overlaps the exponentials of step i, and P.V of step i overlaps
-// the softmax of step i+1; two CTAs share an SM so that one CTA's softmax overlaps the other's MMAs.
+// in registers, so Q.K^T of step i+1 overlaps the exponentials of step i (and the other warp set
+// starts on step i+1 while step i is still being exponentiated), and P.V of step i overlaps the
+// softmax of step i+1; two CTAs share an SM so that one CTA's softmax overlaps the other's MMAs.
 // Every wait is bounded: on expiry the CTA records a code in the status words, raises a shared
 // abort flag and unwinds (TMEM freed).
 #include <cuda_bf16.h>
@@ -119,17 +122,15 @@ __device__ __forceinline__ void report_timeout(const AttnParams& p, volatile int
   *abort_flag = 1;
 }
 
-// Optional cycle accounting of one softmax warp (diagnostic builds only: -DPARO_ATTN_TRACE).
-#ifdef PARO_ATTN_TRACE
-__device__ unsigned long long g_trace[16];
-#define TR_DECL long long tr_acc[6] = {0, 0, 0, 0, 0, 0}, tr_t = 0
-#define TR_MARK tr_t = clock64()
-#define TR_ACC(k) do { const long long n__ = clock64(); tr_acc[k] += n__ - tr_t; tr_t = n__; } while (0)
-#else
-#define TR_DECL do { } while (0)
-#define TR_MARK do { } while (0)
-#define TR_ACC(k) do { } while (0)
-#endif
+// Hand-off of a value between two warps through shared memory (release/acquire at CTA scope).
+__device__ __forceinline__ int ld_acquire_shared(const volatile int* ptr) {
+  int v;
+  asm volatile("ld.acquire.cta.shared.b32 %0, [%1];" : "=r"(v) : "r"(smem_u32(const_cast<const int*>(ptr))) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_shared(volatile int* ptr, int v) {
+  asm volatile("st.release.cta.shared.b32 [%0], %1;" ::"r"(smem_u32(const_cast<int*>(ptr))), "r"(v) : "memory");
+}
 
 #define ATT_WAIT(bar, parity, where, iter)                                   \
   if (!mbar_wait_bounded((bar), (parity), abort_flag, WAIT_LIMIT)) {         \
@@ -150,23 +151,26 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
   uint8_t* sK = smem;
   uint8_t* sV = sK + KST * Cfg::K_BYTES;
   uint8_t* aux = smem + Cfg::TILE_BYTES;
-  uint64_t* bar_q = reinterpret_cast<uint64_t*>(aux);   // [1]    Q tile stored in TMEM (softmax -> MMA issuer)
-  uint64_t* bar_kfull = bar_q + 1;                      // [KST]  K tile landed
-  uint64_t* bar_qkdone = bar_kfull + KST;               // [KST]  Q.K^T of the tile in this K stage finished:
-                                                        //        scores ready (softmax) and K stage free (producer)
-  uint64_t* bar_vfull = bar_qkdone + KST;               // [VST]  V tile landed
-  uint64_t* bar_pvdone = bar_vfull + VST;               // [VST]  P.V of the tile in this V stage finished:
-                                                        //        O up to date (softmax) and V stage free (producer)
-  uint64_t* bar_pready = bar_pvdone + VST;              // [2]    P of one half written (softmax -> P.V issuer)
-  uint64_t* bar_sfree = bar_pready + 2;                 // [2]    scores of one half copied to registers
-                                                        //        (softmax -> Q.K^T issuer)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_sfree + 2);
+  // mbarriers.  [h][par]: one per half of the pair and per parity of the step index, so that each
+  // barrier is arrived on and waited for by the same parties in every phase.
+  uint64_t* bar_q = reinterpret_cast<uint64_t*>(aux);   // [1]     Q tile stored in TMEM
+  uint64_t* bar_kfull = bar_q + 1;                      // [KST]   K tile landed
+  uint64_t* bar_kfree = bar_kfull + KST;                // [KST]   the Q.K^T that read the K stage finished
+  uint64_t* bar_vfull = bar_kfree + KST;                // [VST]   V tile landed
+  uint64_t* bar_vfree = bar_vfull + VST;                // [VST]   the P.V that read the V stage finished
+  uint64_t* bar_sready = bar_vfree + VST;               // [2][2]  scores of (half, step parity) in TMEM
+  uint64_t* bar_sfree = bar_sready + 4;                 // [2][2]  ... copied to registers
+  uint64_t* bar_pready = bar_sfree + 4;                 // [2][2]  P of (half, step parity) written
+  uint64_t* bar_pvdone = bar_pready + 4;                // [2][2]  P.V of (half, step parity) finished
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_pvdone + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* s_mstep = abort_flag + 1;                  // [4]  steps whose row maxima are published, per quadrant
   float* s_vscale = reinterpret_cast<float*>(aux + 512);   // [D]
   float* s_vm = s_vscale + D;                              // [D]
-  float* s_xchg = reinterpret_cast<float*>(aux + 1536);    // [2 buffers][2 column halves][128 rows]
-  static_assert(512 + 2 * D * 4 <= 1536 && 1536 + 2 * 2 * 128 * 4 <= Cfg::AUX_BYTES, "aux area too small");
-  static_assert((5 + 2 * KST + 2 * VST) * 8 + 8 <= 512, "barrier area too small");
+  volatile float* s_mrow = reinterpret_cast<volatile float*>(aux + 1536);   // [128] running row maximum
+  float* s_xl = reinterpret_cast<float*>(aux + 2048);                       // [2][128] row-sum exchange
+  static_assert(512 + 2 * D * 4 <= 1536 && 2048 + 2 * 128 * 4 <= Cfg::AUX_BYTES, "aux area too small");
+  static_assert((17 + 2 * KST + 2 * VST) * 8 + 8 + 20 <= 512, "barrier area too small");
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int bh = blockIdx.x / p.npairs, pair = blockIdx.x % p.npairs;
@@ -184,15 +188,18 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
     mbar_init(bar_q, 4);
     for (int i = 0; i < KST; ++i) {
       mbar_init(bar_kfull + i, 1);
-      mbar_init(bar_qkdone + i, 1);
+      mbar_init(bar_kfree + i, 1);
     }
     for (int i = 0; i < VST; ++i) {
       mbar_init(bar_vfull + i, 1);
-      mbar_init(bar_pvdone + i, 1);
+      mbar_init(bar_vfree + i, 1);
     }
-    for (int h = 0; h < 2; ++h) {   // four warps per half arrive
-      mbar_init(bar_pready + h, ATT_SOFTMAX_THREADS / 64);
-      mbar_init(bar_sfree + h, ATT_SOFTMAX_THREADS / 64);
+    for (int i = 0; i < 4; ++i) {
+      mbar_init(bar_sready + i, 1);
+      mbar_init(bar_sfree + i, 2);    // the two warps (lane quadrants) of a half in one warp set
+      mbar_init(bar_pready + i, 2);
+      mbar_init(bar_pvdone + i, 1);
+      s_mstep[i] = 0;
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -218,14 +225,11 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
           if (i >= (h ? n_b : n_a)) continue;
           const int t = seq(i, h), st = t % KST, use = t / KST;
           const int kb = p.cols[(h ? b0 : a0) + i];
-          if (use > 0 && !mbar_wait_bounded(bar_qkdone + st, (use - 1) & 1, abort_flag, WAIT_LIMIT)) {
+          if (use > 0 && !mbar_wait_bounded(bar_kfree + st, (use - 1) & 1, abort_flag, WAIT_LIMIT)) {
             report_timeout(p, abort_flag, 1, i);
             ok = false;
             break;
           }
-#ifdef PARO_ABL_NO_TMA
-          if (use > 0) { mbar_arrive(bar_kfull + st); continue; }
-#endif
           mbar_arrive_expect_tx(bar_kfull + st, Cfg::K_BYTES);
           tma_load_3d(sK + st * Cfg::K_BYTES, &tm_k, 0, kb * 64, bh, bar_kfull + st);
         }
@@ -239,14 +243,11 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
           if (i >= (h ? n_b : n_a)) continue;
           const int t = seq(i, h), st = t % VST, use = t / VST;
           const int kb = p.cols[(h ? b0 : a0) + i];
-          if (use > 0 && !mbar_wait_bounded(bar_pvdone + st, (use - 1) & 1, abort_flag, WAIT_LIMIT)) {
+          if (use > 0 && !mbar_wait_bounded(bar_vfree + st, (use - 1) & 1, abort_flag, WAIT_LIMIT)) {
             report_timeout(p, abort_flag, 9, i);
             ok = false;
             break;
           }
-#ifdef PARO_ABL_NO_TMA
-          if (use > 0) { mbar_arrive(bar_vfull + st); continue; }
-#endif
           mbar_arrive_expect_tx(bar_vfull + st, Cfg::V_BYTES);
           tma_load_3d(sV + st * Cfg::V_BYTES, &tm_v, kb * 64, 0, bh, bar_vfull + st);
         }
@@ -264,7 +265,7 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
             if (i >= (h ? n_b : n_a)) continue;
             const int t = seq(i, h), st = t % KST;
             // this half's scores of step i-1 are in registers, its rows of S may be overwritten
-            if ((i > 0 && !mbar_wait_bounded(bar_sfree + h, (i - 1) & 1, abort_flag, WAIT_LIMIT)) ||
+            if ((i > 0 && !mbar_wait_bounded(bar_sfree + 2 * h + ((i - 1) & 1), ((i - 1) >> 1) & 1, abort_flag, WAIT_LIMIT)) ||
                 !mbar_wait_bounded(bar_kfull + st, (t / KST) & 1, abort_flag, WAIT_LIMIT)) {
               report_timeout(p, abort_flag, 3, i);
               ok = false;
@@ -276,7 +277,8 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
 #pragma unroll
             for (int k = 0; k < D / 32; ++k)
               mma_i8_ts_masked(tS, tQ + 8 * k, desc_advance(dK, 32 * k), IDESC_QK, k > 0, lo, lo, hi, hi);
-            mma_commit(bar_qkdone + st);
+            mma_commit(bar_kfree + st);
+            mma_commit(bar_sready + 2 * h + (i & 1));
           }
         }
       } while (false);
@@ -288,7 +290,7 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
         for (int h = 0; h < 2; ++h) {
           if (i >= (h ? n_b : n_a)) continue;
           const int t = seq(i, h), st = t % VST;
-          if (!mbar_wait_bounded(bar_pready + h, i & 1, abort_flag, WAIT_LIMIT) ||
+          if (!mbar_wait_bounded(bar_pready + 2 * h + (i & 1), (i >> 1) & 1, abort_flag, WAIT_LIMIT) ||
               !mbar_wait_bounded(bar_vfull + st, (t / VST) & 1, abort_flag, WAIT_LIMIT)) {
             report_timeout(p, abort_flag, 5, i);
             ok = false;
@@ -301,7 +303,8 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
           for (int k = 0; k < 4; ++k)
             mma_f16_ts_masked(tO, tP + 8 * k, desc_advance(dV, 32 * k), IDESC_PV, (i > 0 || k > 0) ? 1u : 0u, lo, lo, hi,
                               hi);
-          mma_commit(bar_pvdone + st);
+          mma_commit(bar_vfree + st);
+          mma_commit(bar_pvdone + 2 * h + (i & 1));
         }
       }
     }
@@ -309,7 +312,7 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
     // ------------------------------------------------------------------ softmax + epilogue
     asm volatile("setmaxnreg.inc.sync.aligned.u32 104;");
     const int qd = warp & 3;                 // TMEM lane quadrant this warp may touch
-    const int ch = warp >> 2;                // which 32 score columns (and which half of O's columns)
+    const int set = warp >> 2;               // warp set: steps of this parity; also which half of O's columns
     const int r = qd * 32 + lane;            // row inside the 128-row tile
     const int half = qd >> 1;                // which q-block of the pair
     const uint32_t lane_off = (uint32_t)(qd * 32) << 16;
@@ -322,7 +325,7 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
     named_barrier(1, ATT_SOFTMAX_THREADS);
 
     const int tok = pair * 128 + r;
-    if (ch == 0) {
+    if (set == 0) {
       // this thread's query row goes to TMEM (four int8 per 32-bit column); rows past the end are zero
       uint32_t qrow[D / 4];
       const uint4* src = reinterpret_cast<const uint4*>(p.q8 + ((size_t)bh * p.N + (tok < p.N ? tok : 0)) * D);
@@ -339,108 +342,139 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
     }
     const int per_bh = p.nb * (64 / p.q_group);
     const float rowscale = (tok < p.N ? p.q_scale[(size_t)bh * per_bh + tok / p.q_group] : 0.f) * p.scale_log2;
-    float m = -INFINITY, l = 0.f;   // l: this thread's share of the row sum
+    // l: this thread's share of the row sum (the steps of its parity), relative to the maximum m_l
+    float m_l = -INFINITY, l = 0.f;
     bool ok = true;
-    // A parity wait can only tell "the phase before the current one is over"; a waiter may skip
-    // phases of a ring barrier only because the rings are at least three deep and tiles complete
-    // in order, so the barrier is never more than one phase away from the one waited for.
-    auto wait_tile = [&](uint64_t* bars, int depth, int t, int code, int i) {
-      const bool good = __all_sync(0xffffffffu, mbar_wait_bounded(bars + t % depth, (t / depth) & 1, abort_flag, WAIT_LIMIT));
+    auto wait_bar = [&](uint64_t* bar, int phase, int code, int i) {
+      const bool good = __all_sync(0xffffffffu, mbar_wait_bounded(bar, phase & 1, abort_flag, WAIT_LIMIT));
       if (!good) report_timeout(p, abort_flag, code, i);
       tc_fence_after();
       return good;
     };
+    uint64_t* const my_sready = bar_sready + 2 * half + set;
+    uint64_t* const my_sfree = bar_sfree + 2 * half + set;
+    uint64_t* const my_pready = bar_pready + 2 * half + set;
+    uint64_t* const prev_pvdone = bar_pvdone + 2 * half + (set ^ 1);   // P.V of the steps of the other parity
     const float* kscale_bh = p.k_scale + (size_t)bh * p.nb;
-    int kb_next = n_mine > 0 ? my_cols[0] : 0;
-    float ks_next = n_mine > 0 ? kscale_bh[kb_next] : 0.f;
-    TR_DECL;
-    for (int i = 0; i < n_mine; ++i) {   // the two halves only meet in the issuers' queues
-      TR_MARK;
+    int kb_next = set < n_mine ? my_cols[set] : 0;
+    float ks_next = set < n_mine ? kscale_bh[kb_next] : 0.f;
+    for (int i = set; i < n_mine; i += 2) {   // the two halves only meet in the issuers' queues
       const int kb = kb_next;
       const float kscale = ks_next;
-      if (i + 1 < n_mine) {   // fetched one step ahead so that the loads are off the critical path
-        kb_next = my_cols[i + 1];
+      if (i + 2 < n_mine) {   // fetched one step ahead so that the loads are off the critical path
+        kb_next = my_cols[i + 2];
         ks_next = kscale_bh[kb_next];
       }
-#ifndef PARO_ABL_FREE_RUN
-      ok = wait_tile(bar_qkdone, KST, seq(i, half), 6, i);
+      ok = wait_bar(my_sready, i >> 1, 6, i);
       if (!ok) break;
-#endif
-      TR_ACC(0);
-      uint32_t pk[16];
-      bool pv_consumed = (i == 0);
+      float f[64];
       {
-        float f[32];
-        {
-          uint32_t s[32];
-          tmem_ld32(tS + lane_off + 32 * ch, s);
+        uint32_t s[64];
+        tmem_ld32(tS + lane_off, s);
+        tmem_ld32(tS + lane_off + 32u, s + 32);
+        tmem_wait_ld();
+        // the scores are in registers: let the issuer overwrite S with this half's next step
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(my_sfree);
+        // int32 scores -> fp32 (exact: |s| < 2^24)
+#pragma unroll
+        for (int j = 0; j < 64; ++j) f[j] = (float)(int)s[j];
+      }
+#ifdef PARO_ABL_NO_SOFTMAX
+      {
+        uint32_t pk0[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) pk0[j] = __float_as_uint(f[j] + f[j + 16] + f[j + 32] + f[j + 48]) & 0x3c003c00u;
+        if (i > 0) ok = wait_bar(prev_pvdone, (i - 1) >> 1, 7, i);
+        if (!ok) break;
+        tmem_st16(tP + lane_off, pk0);
+        tmem_st16(tP + lane_off + 16, pk0);
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(my_pready);
+        if (lane == 0 && i + 1 >= n_mine) s_mrow[r] = 0.f;
+        l += 1.f;
+        continue;
+      }
+#endif
+      const int valid = min(64, p.N - kb * 64);   // columns inside the sequence
+      if (valid < 64) {
+#pragma unroll
+        for (int j = 0; j < 64; ++j)
+          if (j >= valid) f[j] = -INFINITY;
+      }
+      float mx4[4] = {f[0], f[1], f[2], f[3]};   // four independent chains of 3-input max
+#pragma unroll
+      for (int j = 4; j < 64; j += 8) {
+        mx4[0] = max3(mx4[0], f[j], f[j + 1]);
+        mx4[1] = max3(mx4[1], f[j + 2], f[j + 3]);
+        if (j + 4 < 64) {
+          mx4[2] = max3(mx4[2], f[j + 4], f[j + 5]);
+          mx4[3] = max3(mx4[3], f[j + 6], f[j + 7]);
+        }
+      }
+      const float sc = rowscale * kscale;
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sc;
+      // The running maximum of the row passes between the two threads that share it through shared
+      // memory: step i reads what step i-1 (the other warp set) published.
+      float m_old = -INFINITY;
+      if (i > 0) {
+        bool seen = ld_acquire_shared(s_mstep + qd) >= i;
+        if (!seen) {
+          const long long t0 = clock64();
+          while (!(seen = ld_acquire_shared(s_mstep + qd) >= i)) {
+            if (*abort_flag || clock64() - t0 > WAIT_LIMIT) break;
+          }
+        }
+        if (!__all_sync(0xffffffffu, seen)) {
+          report_timeout(p, abort_flag, 10, i);
+          ok = false;
+          break;
+        }
+        m_old = s_mrow[r];
+      }
+      float m_new = m_old;
+      bool resc = false;
+      if (mx > m_old + RESCALE_TAU) {   // lazy: the maximum only moves when it grows by more than 2^tau
+        m_new = mx;
+        resc = m_old > -INFINITY;
+      }
+      s_mrow[r] = m_new;
+      __syncwarp();
+      if (lane == 0) st_release_shared(s_mstep + qd, i + 1);
+      if (m_new != m_l) {
+        l *= ex2_approx(m_l - m_new);     // 0 when m_l = -inf
+        m_l = m_new;
+      }
+      bool pv_consumed = (i == 0);
+      if (__any_sync(0xffffffffu, resc)) {  // O may only be touched once this half's previous P.V has landed
+        pv_consumed = true;
+        ok = wait_bar(prev_pvdone, (i - 1) >> 1, 7, i);
+        if (!ok) break;
+        const float alpha = resc ? ex2_approx(m_old - m_new) : 1.f;
+#pragma unroll
+        for (int c = 0; c < D / 16; ++c) {  // the thread whose step moved the maximum rescales the whole row
+          uint32_t o[16];
+          const uint32_t addr = tO + lane_off + (uint32_t)(16 * c);
+          tmem_ld16(addr, o);
           tmem_wait_ld();
-          TR_ACC(1);
-          // the scores are in registers: let the issuer overwrite S with the next step's
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bar_sfree + half);
-          // int32 scores -> fp32 (exact: |s| < 2^24)
 #pragma unroll
-          for (int j = 0; j < 32; ++j) f[j] = (float)(int)s[j];
+          for (int j = 0; j < 16; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
+          tmem_st16(addr, o);
         }
-        const int valid = min(64, p.N - kb * 64) - 32 * ch;   // columns of mine inside the sequence
-        if (valid < 32) {
+        tmem_wait_st();
+      }
+      const uint64_t sc2 = pack2(sc, sc), negm2 = pack2(-m_new, -m_new);
+      uint64_t sum2[2] = {0ull, 0ull};
 #pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (j >= valid) f[j] = -INFINITY;
-        }
-        float mx4[4] = {f[0], f[1], f[2], f[3]};   // four independent chains of 3-input max
-#pragma unroll
-        for (int j = 4; j < 32; j += 8) {
-          mx4[0] = max3(mx4[0], f[j], f[j + 1]);
-          mx4[1] = max3(mx4[1], f[j + 2], f[j + 3]);
-          if (j + 4 < 32) {
-            mx4[2] = max3(mx4[2], f[j + 4], f[j + 5]);
-            mx4[3] = max3(mx4[3], f[j + 6], f[j + 7]);
-          }
-        }
-        const float my_max = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-        TR_ACC(2);
-        // the row's other 32 columns belong to the thread of warp (w ^ 4) with the same lane
-        float* xb = s_xchg + (i & 1) * 256;
-        const float sc = rowscale * kscale;
-        xb[ch * 128 + r] = my_max;
-        named_barrier(2 + qd, 64);
-        const float mx = fmaxf(my_max, xb[(ch ^ 1) * 128 + r]) * sc;
-        float alpha = 1.f;
-        bool resc = false;
-        if (mx > m + RESCALE_TAU) {
-          alpha = ex2_approx(m - mx);     // 0 when m = -inf
-          resc = m > -INFINITY;
-          m = mx;
-          l *= alpha;
-        }
-        if (__any_sync(0xffffffffu, resc)) {  // O may only be touched once this half's previous P.V has landed
-          if (!pv_consumed) {
-            pv_consumed = true;
-            ok = wait_tile(bar_pvdone, VST, seq(i - 1, half), 7, i);
-            if (!ok) break;
-          }
-#pragma unroll
-          for (int c = 0; c < D / 32; ++c) {  // this thread owns half of the row's O columns
-            uint32_t o[16];
-            const uint32_t addr = tO + lane_off + (uint32_t)(ch * (D / 2) + 16 * c);
-            tmem_ld16(addr, o);
-            tmem_wait_ld();
-#pragma unroll
-            for (int j = 0; j < 16; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
-            tmem_st16(addr, o);
-          }
-          tmem_wait_st();
-        }
-        TR_ACC(3);
-        const uint64_t sc2 = pack2(sc, sc), negm2 = pack2(-m, -m);
-        uint64_t sum2[2] = {0ull, 0ull};
+      for (int c = 0; c < 2; ++c) {
+        uint32_t pk[16];
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
           float x0, x1;
-          unpack2(fma2(pack2(f[2 * j], f[2 * j + 1]), sc2, negm2), x0, x1);
+          unpack2(fma2(pack2(f[32 * c + 2 * j], f[32 * c + 2 * j + 1]), sc2, negm2), x0, x1);
 #ifdef PARO_ABL_NO_MUFU
           const float p0 = x0, p1 = x1;
 #else
@@ -450,54 +484,45 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
           const __half2 h2 = __floats2half2_rn(p0, p1);
           pk[j] = *reinterpret_cast<const uint32_t*>(&h2);
         }
-        float sa, sb;
-        unpack2(add2(sum2[0], sum2[1]), sa, sb);
-        l += sa + sb;
-        TR_ACC(4);
+        // P of this half is rewritten only after the P.V that read its previous contents (the other
+        // warp set's step) has finished
+        if (c == 0 && !pv_consumed) ok = wait_bar(prev_pvdone, (i - 1) >> 1, 7, i);
+        tmem_st16(tP + lane_off + 16 * c, pk);   // fp16 P: two values per 32-bit column
       }
-      // P of this half is rewritten only after the P.V that read its previous contents has finished
-      // (that P.V was issued a whole softmax ago, so this wait normally returns at once)
-      if (!pv_consumed) {
-        ok = wait_tile(bar_pvdone, VST, seq(i - 1, half), 7, i);
-        if (!ok) break;
-      }
-      tmem_st16(tP + lane_off + 16 * ch, pk);   // fp16 P: two values per 32-bit column
+      if (!ok) break;
+      float sa, sb;
+      unpack2(add2(sum2[0], sum2[1]), sa, sb);
+      l += sa + sb;
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar_pready + half);   // one arrival per warp
-      TR_ACC(5);
+      if (lane == 0) mbar_arrive(my_pready);   // one arrival per warp
     }
-#ifdef PARO_ATTN_TRACE
-    if (lane == 0 && warp == 0) {
-      for (int k = 0; k < 6; ++k) atomicAdd(&g_trace[k], (unsigned long long)tr_acc[k]);
-      atomicAdd(&g_trace[6], (unsigned long long)n_mine);
-      atomicAdd(&g_trace[7], (unsigned long long)n_steps);
-    }
-#endif
 
     // epilogue (the TMEM loads are warp-collective: every lane of the warp executes them, rows past
     // the end of the sequence only skip the store)
-    if (ok && n_mine > 0) ok = wait_tile(bar_pvdone, VST, seq(n_mine - 1, half), 8, n_mine);
-    // row sum = both threads' shares (reached by every softmax thread, also after a failed wait)
-    float* xl = s_xchg;
+    if (ok && n_mine > 0) ok = wait_bar(bar_pvdone + 2 * half + ((n_mine - 1) & 1), (n_mine - 1) >> 1, 8, n_mine);
+    // final maximum and row sum = both threads' shares (reached by every softmax thread, also
+    // after a failed wait)
     named_barrier(1, ATT_SOFTMAX_THREADS);
-    xl[ch * 128 + r] = l;
+    const float m = n_mine > 0 ? s_mrow[r] : -INFINITY;
+    if (m_l != m) l *= ex2_approx(m_l - m);
+    s_xl[set * 128 + r] = l;
     named_barrier(1, ATT_SOFTMAX_THREADS);
-    l += xl[(ch ^ 1) * 128 + r];
+    l += s_xl[(set ^ 1) * 128 + r];
     if (ok) {
       const int b = bh / p.H, h = bh % p.H;
       const bool live = tok < p.N;
       int dst = tok;
       if (live && p.inv_idx && tok >= p.n_text)
         dst = p.n_text + p.inv_idx[(size_t)h * (p.N - p.n_text) + (tok - p.n_text)];
-      OutT* orow = static_cast<OutT*>(p.out) + b * p.osb + h * p.osh + (int64_t)dst * p.osn + ch * (D / 2);
+      OutT* orow = static_cast<OutT*>(p.out) + b * p.osb + h * p.osh + (int64_t)dst * p.osn + set * (D / 2);
       const float inv_l = l > 0.f ? 1.f / l : 0.f;
 #pragma unroll
       for (int c = 0; c < D / 64; ++c) {
         uint32_t o[32];
         if (n_mine > 0) {
-          tmem_ld32(tO + lane_off + (uint32_t)(ch * (D / 2) + 32 * c), o);
+          tmem_ld32(tO + lane_off + (uint32_t)(set * (D / 2) + 32 * c), o);
           tmem_wait_ld();
         } else {
 #pragma unroll
@@ -506,7 +531,7 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
         uint32_t w[16];
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
-          const int d0 = ch * (D / 2) + 32 * c + 2 * j;
+          const int d0 = set * (D / 2) + 32 * c + 2 * j;
           const float a0f = l > 0.f ? fmaf(__uint_as_float(o[2 * j]) * inv_l, s_vscale[d0], s_vm[d0]) : 0.f;
           const float a1f = l > 0.f ? fmaf(__uint_as_float(o[2 * j + 1]) * inv_l, s_vscale[d0 + 1], s_vm[d0 + 1]) : 0.f;
           OutT t2[2] = {F16Traits<OutT>::from_float(a0f), F16Traits<OutT>::from_float(a1f)};
@@ -518,7 +543,7 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
             *reinterpret_cast<uint4*>(orow + 32 * c + 8 * j) = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
         }
       }
-      if (live && ch == 0 && p.lse)
+      if (live && set == 0 && p.lse)
         p.lse[(size_t)bh * p.N + dst] = l > 0.f ? (log2f(l) + m) * 0.6931471805599453f : -INFINITY;
     }
   }
