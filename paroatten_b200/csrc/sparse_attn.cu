@@ -381,24 +381,6 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
 #pragma unroll
         for (int j = 0; j < 64; ++j) f[j] = (float)(int)s[j];
       }
-#ifdef PARO_ABL_NO_SOFTMAX
-      {
-        uint32_t pk0[16];
-#pragma unroll
-        for (int j = 0; j < 16; ++j) pk0[j] = __float_as_uint(f[j] + f[j + 16] + f[j + 32] + f[j + 48]) & 0x3c003c00u;
-        if (i > 0) ok = wait_bar(prev_pvdone, (i - 1) >> 1, 7, i);
-        if (!ok) break;
-        tmem_st16(tP + lane_off, pk0);
-        tmem_st16(tP + lane_off + 16, pk0);
-        tmem_wait_st();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(my_pready);
-        if (lane == 0 && i + 1 >= n_mine) s_mrow[r] = 0.f;
-        l += 1.f;
-        continue;
-      }
-#endif
       const int valid = min(64, p.N - kb * 64);   // columns inside the sequence
       if (valid < 64) {
 #pragma unroll
@@ -475,11 +457,7 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
         for (int j = 0; j < 16; ++j) {
           float x0, x1;
           unpack2(fma2(pack2(f[32 * c + 2 * j], f[32 * c + 2 * j + 1]), sc2, negm2), x0, x1);
-#ifdef PARO_ABL_NO_MUFU
-          const float p0 = x0, p1 = x1;
-#else
           const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);   // 2^-inf = 0 for masked columns
-#endif
           sum2[j & 1] = add2(sum2[j & 1], pack2(p0, p1));
           const __half2 h2 = __floats2half2_rn(p0, p1);
           pk[j] = *reinterpret_cast<const uint32_t*>(&h2);
@@ -650,16 +628,6 @@ extern "C" int paro_sparse_attn(const int8_t* q8, const int8_t* k8, const uint16
                                : launch_attn<64, __nv_bfloat16>(q8, k8, v16, p, s);
 }
 
-#ifdef PARO_ATTN_TRACE
-extern "C" int paro_debug_trace(unsigned long long* host16, int reset) {
-  if (host16) cudaMemcpyFromSymbol(host16, paro::g_trace, sizeof(unsigned long long) * 16);
-  if (reset) {
-    unsigned long long z[16] = {0};
-    cudaMemcpyToSymbol(paro::g_trace, z, sizeof(z));
-  }
-  return 0;
-}
-#endif
 
 extern "C" int paro_status_poll(const int32_t* status, int32_t* host_out, paro_stream_t stream) {
   PARO_REQUIRE(status, PARO_EINVAL, "paro_status_poll: null pointer");
