@@ -275,7 +275,7 @@ def main():
         ho = torch.empty(out.shape, dtype=out.dtype).pin_memory()
         pipe = pb.HostPipelinedAttention(orders_all[h0:h1], mask_all[h0:h1], (B, Hl, N, D), torch.bfloat16,
                                          grid_fhw=wl["grid"], n_text=n_text, rope=rope,
-                                         heads_per_group=max(1, min(5, Hl)), device=dev)
+                                         device=dev)
 
         def e2e_step():
             pipe(hq, hk, hv, ho)

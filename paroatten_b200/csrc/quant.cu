@@ -4,6 +4,7 @@
 #include <cuda_fp8.h>
 
 #include <mutex>
+#include <type_traits>
 
 #include "common.cuh"
 #include "perm.cuh"
@@ -21,22 +22,49 @@ struct Gather {
   RopeArgs rope;
 };
 
+// GM (compile time): 0 plain input; 1 reordering only; 2 reordering + fp32 rotation; 3 reordering +
+// fp64 rotation.  A kernel instance only carries the code and registers of its own mode.
+enum { GM_PLAIN = 0, GM_REORDER = 1, GM_ROPE_F32 = 2, GM_ROPE_F64 = 3 };
+
+inline int gather_mode(const Gather& g) {
+  if (!g.enabled) return GM_PLAIN;
+  if (g.rope.mode == PARO_ROPE_REAL_F32) return GM_ROPE_F32;
+  if (g.rope.mode == PARO_ROPE_COMPLEX_F64) return GM_ROPE_F64;
+  return GM_REORDER;
+}
+
+template <int GM>
 struct GatherCtx {
   const Gather& g;
   PermDecoder dec;
   __device__ GatherCtx(const Gather& g_, int h)
-      : g(g_), dec(g_.enabled && g_.order_ids ? g_.order_ids[h] : 0, g_.F, g_.Hh, g_.W) {}
+      : g(g_), dec(GM != GM_PLAIN && g_.order_ids ? g_.order_ids[h] : 0, g_.F, g_.Hh, g_.W) {}
   // source token of row `tok`; f < 0 for rows that are not rotated (text tokens, or no gather)
   __device__ __forceinline__ int source(int tok, int& f, int& y, int& x) const {
     f = y = x = -1;
-    if (!g.enabled || tok < g.n_text) return tok;
+    if constexpr (GM == GM_PLAIN) return tok;
+    if (tok < g.n_text) return tok;
     const int src = g.n_text + dec.source(tok - g.n_text, f, y, x);
     return src;
   }
   template <typename T> __device__ __forceinline__ void rotate(Pack8<T>& v, int c8, int D, int f, int y, int x) const {
-    if (g.enabled && g.rope.mode != PARO_ROPE_NONE && f >= 0) rotate8<T>(v, c8, D, f, y, x, g.F, g.Hh, g.rope);
+    if constexpr (GM == GM_ROPE_F32) {
+      if (f >= 0) rotate8<T, PARO_ROPE_REAL_F32>(v, c8, D, f, y, x, g.F, g.Hh, g.rope);
+    } else if constexpr (GM == GM_ROPE_F64) {
+      if (f >= 0) rotate8<T, PARO_ROPE_COMPLEX_F64>(v, c8, D, f, y, x, g.F, g.Hh, g.rope);
+    }
   }
 };
+
+// Calls `fn(std::integral_constant<int, GM>)` for the mode of `g`.
+template <typename Fn> void dispatch_gather(const Gather& g, Fn&& fn) {
+  switch (gather_mode(g)) {
+    case GM_REORDER: fn(std::integral_constant<int, GM_REORDER>{}); break;
+    case GM_ROPE_F32: fn(std::integral_constant<int, GM_ROPE_F32>{}); break;
+    case GM_ROPE_F64: fn(std::integral_constant<int, GM_ROPE_F64>{}); break;
+    default: fn(std::integral_constant<int, GM_PLAIN>{}); break;
+  }
+}
 
 constexpr int STATS_CHUNK = 512;  // tokens reduced by one CTA of the channel-statistics pass
 
@@ -49,7 +77,7 @@ struct ChannelPartial {
 // Pass 1 of the per-channel reductions: per (b,h, chunk of tokens) the fp64 sum, max and min of
 // every channel.  Thread = one 8-channel slice of a token row; rows of the chunk are walked in a
 // fixed order and the cross-thread reduction is sequential, so results do not depend on timing.
-template <typename T, int D>
+template <typename T, int D, int GM>
 __global__ void __launch_bounds__(256)
 channel_stats_kernel(const T* __restrict__ x, int H, int N, int64_t sb, int64_t sh, int64_t sn,
                      ChannelPartial* __restrict__ part, int chunks, const Gather gather) {
@@ -62,23 +90,32 @@ channel_stats_kernel(const T* __restrict__ x, int H, int N, int64_t sb, int64_t 
   const int c8 = (threadIdx.x % TPR) * 8, r = threadIdx.x / TPR;
   const int t0 = blockIdx.x * STATS_CHUNK, t1 = min(N, t0 + STATS_CHUNK);
   const T* base = x + b * sb + h * sh;
-  const GatherCtx gc(gather, h);
+  const GatherCtx<GM> gc(gather, h);
   double sum[8];
   float mx[8], mn[8];
 #pragma unroll
   for (int j = 0; j < 8; ++j) { sum[j] = 0.0; mx[j] = -INFINITY; mn[j] = INFINITY; }
-  for (int t = t0 + r; t < t1; t += ROWS) {
-    Pack8<T> v;
-    int gf, gy, gx;
-    const int src = gc.source(t, gf, gy, gx);
-    v.v = *reinterpret_cast<const uint4*>(base + (size_t)src * sn + c8);
-    gc.rotate(v, c8, D, gf, gy, gx);
+  // four rows are in flight per thread; they are accumulated in the order of a plain loop
+  for (int t = t0 + r; t < t1; t += 4 * ROWS) {
+    Pack8<T> v[4];
+    int gf[4], gy[4], gx[4];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const float f = F16Traits<T>::to_float(v.e[j]);
-      sum[j] += (double)f;
-      mx[j] = fmaxf(mx[j], f);
-      mn[j] = fminf(mn[j], f);
+    for (int u = 0; u < 4; ++u) {
+      const int tu = t + u * ROWS;
+      gf[u] = gy[u] = gx[u] = -1;
+      if (tu < t1) v[u].v = *reinterpret_cast<const uint4*>(base + (size_t)gc.source(tu, gf[u], gy[u], gx[u]) * sn + c8);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      if (t + u * ROWS >= t1) break;
+      gc.rotate(v[u], c8, D, gf[u], gy[u], gx[u]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float f = F16Traits<T>::to_float(v[u].e[j]);
+        sum[j] += (double)f;
+        mx[j] = fmaxf(mx[j], f);
+        mn[j] = fminf(mn[j], f);
+      }
     }
   }
 #pragma unroll
@@ -127,8 +164,8 @@ __global__ void channel_finalize_kernel(const ChannelPartial* __restrict__ part,
 
 // ---------------------------------------------------------------------------------------------
 // INT8: CTA = 128 threads = one 64-token block; warp w owns tokens 16w..16w+15.
-template <typename T, int D, int GROUP>
-__global__ void __launch_bounds__(128)
+template <typename T, int D, int GROUP, int GM>
+__global__ void __launch_bounds__(128, GM == GM_ROPE_F64 ? 4 : (GM == GM_ROPE_F32 ? 5 : 6))
 quant_int8_kernel(const T* __restrict__ x, const T* __restrict__ km, int8_t* __restrict__ out,
                   float* __restrict__ scale, int H, int N, int64_t sb, int64_t sh, int64_t sn,
                   float fold, int n_scale_per_bh, const Gather gather) {
@@ -141,7 +178,7 @@ quant_int8_kernel(const T* __restrict__ x, const T* __restrict__ km, int8_t* __r
   const int c8 = (lane % TPR) * 8;
   const int tok0 = blockIdx.x * 64 + warp * 16 + lane / TPR;
   const T* base = x + b * sb + h * sh;
-  const GatherCtx gc(gather, h);
+  const GatherCtx<GM> gc(gather, h);
 
   float mean[8];
 #pragma unroll
@@ -153,28 +190,44 @@ quant_int8_kernel(const T* __restrict__ x, const T* __restrict__ km, int8_t* __r
     for (int j = 0; j < 8; ++j) mean[j] = F16Traits<T>::to_float(m.e[j]);
   }
 
-  float v[LOADS][8];
+  // the (rotated) rows stay packed in registers; they are widened once for the maximum and once more
+  // for the rounding, which costs a shift per element and halves the registers held across the barrier
+  Pack8<T> row[LOADS];
   float amax = 0.f;
+  auto widen = [&](const Pack8<T>& p, int j) {
+    float f = F16Traits<T>::to_float(p.e[j]);
+    if (km) f = __fsub_rn(f, mean[j]);
+    if (fold != 0.f) f = __fmul_rn(f, fold);
+    return f;
+  };
+  // Each of the warp's 16 tokens is decoded once (source token and grid position) by lane t and
+  // lane t+16, and handed to the threads that load it.
+  int d_src = 0, d_f = -1, d_y = -1, d_x = -1;
+  if constexpr (GM != GM_PLAIN) {
+    const int t = blockIdx.x * 64 + warp * 16 + (lane & 15);
+    if (t < N) d_src = gc.source(t, d_f, d_y, d_x);
+  }
+#pragma unroll
+  for (int i = 0; i < LOADS; ++i) {   // all loads first, so that every row of the thread is in flight at once
+    const int tok = tok0 + i * RPL;
+    row[i].v = make_uint4(0, 0, 0, 0);
+    int src = tok;
+    if constexpr (GM != GM_PLAIN) src = __shfl_sync(0xffffffffu, d_src, i * RPL + lane / TPR);
+    if (tok < N) row[i].v = *reinterpret_cast<const uint4*>(base + (size_t)src * sn + c8);
+  }
 #pragma unroll
   for (int i = 0; i < LOADS; ++i) {
     const int tok = tok0 + i * RPL;
+    if constexpr (GM == GM_ROPE_F32 || GM == GM_ROPE_F64) {
+      const int from = i * RPL + lane / TPR;
+      const int gf = __shfl_sync(0xffffffffu, d_f, from);
+      const int gy = __shfl_sync(0xffffffffu, d_y, from);
+      const int gx = __shfl_sync(0xffffffffu, d_x, from);
+      if (tok < N) gc.rotate(row[i], c8, D, gf, gy, gx);
+    }
     if (tok < N) {
-      Pack8<T> p;
-      int gf, gy, gx;
-      const int src = gc.source(tok, gf, gy, gx);
-      p.v = *reinterpret_cast<const uint4*>(base + (size_t)src * sn + c8);
-      gc.rotate(p, c8, D, gf, gy, gx);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        float f = F16Traits<T>::to_float(p.e[j]);
-        if (km) f = __fsub_rn(f, mean[j]);
-        if (fold != 0.f) f = __fmul_rn(f, fold);
-        v[i][j] = f;
-        amax = fmaxf(amax, fabsf(f));
-      }
-    } else {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) v[i][j] = 0.f;
+      for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(widen(row[i], j)));
     }
   }
 #pragma unroll
@@ -201,7 +254,7 @@ quant_int8_kernel(const T* __restrict__ x, const T* __restrict__ km, int8_t* __r
       // round to nearest even (NaN -> 0), then saturate and pack two values per instruction
       int qi[8];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) qi[j] = __float2int_rn(__fmul_rn(v[i][j], inv));
+      for (int j = 0; j < 8; ++j) qi[j] = __float2int_rn(__fmul_rn(widen(row[i], j), inv));
       uint32_t w[2];
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
@@ -220,7 +273,7 @@ quant_int8_kernel(const T* __restrict__ x, const T* __restrict__ km, int8_t* __r
 // Phase 1 stages the raw tile in shared memory with coalesced 16-byte loads; phase 2 lets
 // consecutive lanes take consecutive channels (conflict-free column reads) and each thread emit a
 // run of tokens of its channel as whole 32-byte sectors.
-template <typename T, int D>
+template <typename T, int D, int GM>
 __global__ void __launch_bounds__(256)
 quant_v_fp8_kernel(const T* __restrict__ v, int H, int N, int npad, int64_t sb, int64_t sh, int64_t sn,
                    const float* __restrict__ inv_tab, const float* __restrict__ mean_tab,
@@ -234,7 +287,7 @@ quant_v_fp8_kernel(const T* __restrict__ v, int H, int N, int npad, int64_t sb, 
   const int t0 = blockIdx.x * 64;
   const T* base = v + b * sb + h * sh;
   {
-    const GatherCtx gc(gather, h);
+    const GatherCtx<GM> gc(gather, h);
     const int c8 = (threadIdx.x % TPR) * 8;
 #pragma unroll
     for (int r = threadIdx.x / TPR; r < 64; r += ROWS) {
@@ -294,10 +347,13 @@ template <typename T>
 void launch_stats(const void* x, int B, int H, int N, int D, int64_t sb, int64_t sh, int64_t sn,
                   ChannelPartial* part, cudaStream_t s, const Gather& g = Gather{}) {
   dim3 grid(stats_chunks(N), B * H);
-  if (D == 128)
-    channel_stats_kernel<T, 128><<<grid, 256, 0, s>>>((const T*)x, H, N, sb, sh, sn, part, stats_chunks(N), g);
-  else
-    channel_stats_kernel<T, 64><<<grid, 256, 0, s>>>((const T*)x, H, N, sb, sh, sn, part, stats_chunks(N), g);
+  dispatch_gather(g, [&](auto gm) {
+    constexpr int GM = decltype(gm)::value;
+    if (D == 128)
+      channel_stats_kernel<T, 128, GM><<<grid, 256, 0, s>>>((const T*)x, H, N, sb, sh, sn, part, stats_chunks(N), g);
+    else
+      channel_stats_kernel<T, 64, GM><<<grid, 256, 0, s>>>((const T*)x, H, N, sb, sh, sn, part, stats_chunks(N), g);
+  });
 }
 
 }  // namespace
@@ -337,11 +393,15 @@ int launch_int8(const void* x, const void* km, int8_t* out, float* scale, int B,
                 int64_t sh, int64_t sn, float fold, int group, cudaStream_t s, const Gather& g = Gather{}) {
   const int nb = (N + 63) / 64;
   dim3 grid(nb, B * H);
-  if (group == 64)
-    quant_int8_kernel<T, D, 64><<<grid, 128, 0, s>>>((const T*)x, (const T*)km, out, scale, H, N, sb, sh, sn, fold, nb, g);
-  else
-    quant_int8_kernel<T, D, 32><<<grid, 128, 0, s>>>((const T*)x, (const T*)km, out, scale, H, N, sb, sh, sn, fold,
-                                                     nb * 2, g);
+  dispatch_gather(g, [&](auto gm) {
+    constexpr int GM = decltype(gm)::value;
+    if (group == 64)
+      quant_int8_kernel<T, D, 64, GM><<<grid, 128, 0, s>>>((const T*)x, (const T*)km, out, scale, H, N, sb, sh, sn, fold,
+                                                           nb, g);
+    else
+      quant_int8_kernel<T, D, 32, GM><<<grid, 128, 0, s>>>((const T*)x, (const T*)km, out, scale, H, N, sb, sh, sn, fold,
+                                                           nb * 2, g);
+  });
   return check_launch("quant_int8_kernel");
 }
 }  // namespace
@@ -377,12 +437,16 @@ int run_v_fp8(const void* v, int B, int H, int N, int D, int64_t sb, int64_t sh,
                                                  smooth ? vm : nullptr, v_scale, inv_tab, mean_tab);
   const int npad = (N + 63) / 64 * 64;
   dim3 grid(npad / 64, B * H);
-  if (D == 128)
-    quant_v_fp8_kernel<T, 128><<<grid, 256, 0, s>>>((const T*)v, H, N, npad, sb, sh, sn, inv_tab, mean_tab, v8,
-                                                    (__half*)v16, g);
-  else
-    quant_v_fp8_kernel<T, 64><<<grid, 256, 0, s>>>((const T*)v, H, N, npad, sb, sh, sn, inv_tab, mean_tab, v8,
-                                                   (__half*)v16, g);
+  dispatch_gather(g, [&](auto gm) {
+    // the V pass never rotates: reordering only
+    constexpr int GM = decltype(gm)::value == GM_PLAIN ? GM_PLAIN : GM_REORDER;
+    if (D == 128)
+      quant_v_fp8_kernel<T, 128, GM><<<grid, 256, 0, s>>>((const T*)v, H, N, npad, sb, sh, sn, inv_tab, mean_tab, v8,
+                                                          (__half*)v16, g);
+    else
+      quant_v_fp8_kernel<T, 64, GM><<<grid, 256, 0, s>>>((const T*)v, H, N, npad, sb, sh, sn, inv_tab, mean_tab, v8,
+                                                         (__half*)v16, g);
+  });
   return check_launch("quant_v_fp8", 3);
 }
 }  // namespace

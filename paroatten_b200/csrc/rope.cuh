@@ -14,7 +14,9 @@ struct RopeArgs {
 // Rotates the four channel pairs held in `x` (channels c8..c8+7 of a token at grid
 // coordinate f,y,x).  Products and sums are rounded separately (no fused multiply-add) so that
 // results equal a plain elementwise evaluation.
-template <typename T>
+// MODE: PARO_ROPE_REAL_F32 or PARO_ROPE_COMPLEX_F64 (compile time, so that a kernel only carries the
+// registers of the arithmetic it uses).
+template <typename T, int MODE>
 __device__ __forceinline__ void rotate8(Pack8<T>& x, int c8, int D, int f, int y, int xw,
                                         int F, int Hh, const RopeArgs& r) {
   const int half = D >> 1;
@@ -23,7 +25,7 @@ __device__ __forceinline__ void rotate8(Pack8<T>& x, int c8, int D, int f, int y
     const int pair = (c8 >> 1) + p;
     const int row = pair < r.pairs_f ? f : (pair < r.pairs_f + r.pairs_h ? F + y : F + Hh + xw);
     const size_t t = (size_t)row * half + pair;
-    if (r.mode == PARO_ROPE_REAL_F32) {
+    if constexpr (MODE == PARO_ROPE_REAL_F32) {
       const float c = static_cast<const float*>(r.cos_tab)[t];
       const float s = static_cast<const float*>(r.sin_tab)[t];
       const float x0 = F16Traits<T>::to_float(x.e[2 * p]);

@@ -9,7 +9,7 @@ namespace paro {
 
 // Block = 256 threads; a thread owns one 16-byte slice of a row and walks ROWS_PER_THREAD rows.
 // blockIdx.x: group of rows, blockIdx.y: b*H + h.
-template <typename T, int D>
+template <typename T, int D, int MODE>
 __global__ void __launch_bounds__(256)
 rope_permute_kernel(const T* __restrict__ in, T* __restrict__ out, int H, int N,
                     int64_t sb, int64_t sh, int64_t sn, int n_text, int F, int Hh, int W,
@@ -54,25 +54,39 @@ rope_permute_kernel(const T* __restrict__ in, T* __restrict__ out, int H, int N,
 #pragma unroll
   for (int i = 0; i < PASSES; ++i) {
     if (dst_row[i] < 0) continue;
-    if (rope.mode != PARO_ROPE_NONE && fy[i] >= 0) rotate8<T>(val[i], c8, D, fy[i], yy[i], xx[i], F, Hh, rope);
+    if constexpr (MODE != PARO_ROPE_NONE) {
+      if (fy[i] >= 0) rotate8<T, MODE>(val[i], c8, D, fy[i], yy[i], xx[i], F, Hh, rope);
+    }
     *reinterpret_cast<uint4*>(dst_base + (size_t)dst_row[i] * D + c8) = val[i].v;
   }
+}
+
+template <typename T, int MODE>
+int launch_rope_mode(const void* in, void* out, int B, int H, int N, int D, int64_t sb, int64_t sh, int64_t sn,
+                     int n_text, int F, int Hh, int W, const int32_t* order_ids, int inverse,
+                     const RopeArgs& rope, cudaStream_t s) {
+  if (D == 128) {
+    dim3 grid((N + 63) / 64, B * H);
+    rope_permute_kernel<T, 128, MODE><<<grid, 256, 0, s>>>((const T*)in, (T*)out, H, N, sb, sh, sn, n_text, F, Hh, W,
+                                                           order_ids, inverse, rope);
+  } else {
+    dim3 grid((N + 127) / 128, B * H);
+    rope_permute_kernel<T, 64, MODE><<<grid, 256, 0, s>>>((const T*)in, (T*)out, H, N, sb, sh, sn, n_text, F, Hh, W,
+                                                          order_ids, inverse, rope);
+  }
+  return check_launch("rope_permute_kernel");
 }
 
 template <typename T>
 int launch_rope(const void* in, void* out, int B, int H, int N, int D, int64_t sb, int64_t sh, int64_t sn,
                 int n_text, int F, int Hh, int W, const int32_t* order_ids, int inverse,
                 const RopeArgs& rope, cudaStream_t s) {
-  if (D == 128) {
-    dim3 grid((N + 63) / 64, B * H);
-    rope_permute_kernel<T, 128><<<grid, 256, 0, s>>>((const T*)in, (T*)out, H, N, sb, sh, sn, n_text, F, Hh, W,
-                                                     order_ids, inverse, rope);
-  } else {
-    dim3 grid((N + 127) / 128, B * H);
-    rope_permute_kernel<T, 64><<<grid, 256, 0, s>>>((const T*)in, (T*)out, H, N, sb, sh, sn, n_text, F, Hh, W,
-                                                    order_ids, inverse, rope);
-  }
-  return check_launch("rope_permute_kernel");
+#define PARO_ROPE_CASE(M) \
+  return launch_rope_mode<T, M>(in, out, B, H, N, D, sb, sh, sn, n_text, F, Hh, W, order_ids, inverse, rope, s)
+  if (rope.mode == PARO_ROPE_REAL_F32) PARO_ROPE_CASE(PARO_ROPE_REAL_F32);
+  if (rope.mode == PARO_ROPE_COMPLEX_F64) PARO_ROPE_CASE(PARO_ROPE_COMPLEX_F64);
+  PARO_ROPE_CASE(PARO_ROPE_NONE);
+#undef PARO_ROPE_CASE
 }
 
 }  // namespace paro

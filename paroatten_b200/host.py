@@ -18,15 +18,36 @@ from .plan import CompactPlan, PermutePlan, compact_plan
 from .rope import RopeTables
 
 
+def head_groups(H: int, heads_per_group: Optional[int] = None) -> List[Tuple[int, int]]:
+    """Cuts H heads into the [h0, h1) groups the pipeline works on.  The host-to-device copies are
+    the slowest stage, so what is left after the last copy -- the last group's kernels and its
+    copy back -- is pure tail: the groups shrink towards the end (g, ..., g, g-1, ..., 2, 1; a remainder
+    goes first, where a short group also shortens the start-up), and the default g gives at least
+    four groups so that a rank with few heads still overlaps its stages."""
+    H = int(H)
+    g = max(1, min(5, (H + 3) // 4)) if heads_per_group is None else max(1, min(int(heads_per_group), H))
+    tail = list(range(g - 1, 0, -1))            # g-1, ..., 2, 1
+    while tail and sum(tail) > H - min(g, H):   # keep at least one full-size group
+        tail.pop(0)
+    body = H - sum(tail)
+    sizes = ([body % g] if body % g else []) + [g] * (body // g) + tail
+    out, h0 = [], 0
+    for n in sizes:
+        out.append((h0, h0 + n))
+        h0 += n
+    return out
+
+
 class HostPipelinedAttention:
     """Set up once per (layer, timestep bin) -- the sparse plan is compacted per head group and
     the staging buffers are allocated here -- then call it with pinned host tensors.
 
     orders: int order ids [H]; mask: bool [H, nb, nb] (shared by the batch);
-    shape = (B, H, N, D) of the host tensors; heads_per_group: heads copied/computed at a time."""
+    shape = (B, H, N, D) of the host tensors; heads_per_group: heads copied/computed at a time
+    (default: see `head_groups`)."""
 
     def __init__(self, orders, mask: torch.Tensor, shape: Tuple[int, int, int, int], dtype, *, grid_fhw,
-                 n_text: int = 0, rope: Optional[RopeTables] = None, heads_per_group: int = 5, device=None,
+                 n_text: int = 0, rope: Optional[RopeTables] = None, heads_per_group: Optional[int] = None, device=None,
                  sm_scale: Optional[float] = None, smooth_k: bool = True, smooth_v: bool = True):
         B, H, N, D = (int(x) for x in shape)
         self.shape, self.dtype = (B, H, N, D), dtype
@@ -38,8 +59,8 @@ class HostPipelinedAttention:
         orders = torch.as_tensor(orders).to(torch.int32)
         if orders.numel() != H:
             raise ValueError("orders must hold one id per head")
-        g = max(1, min(int(heads_per_group), H))
-        self.groups: List[Tuple[int, int]] = [(h0, min(H, h0 + g)) for h0 in range(0, H, g)]
+        self.groups: List[Tuple[int, int]] = head_groups(H, heads_per_group)
+        g = max(h1 - h0 for h0, h1 in self.groups)
         with torch.cuda.device(self.device):
             self.plans: List[CompactPlan] = [compact_plan(mask[h0:h1].to(self.device)) for h0, h1 in self.groups]
             self.pplans = [PermutePlan({"permute": orders[h0:h1].reshape(1, -1)}, self.kw["grid_fhw"], self.device)

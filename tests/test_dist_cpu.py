@@ -74,3 +74,21 @@ def test_ulysses_rejects_uneven_heads():
     # world size comes from the process group; without one, torch raises before any exchange
     with pytest.raises(Exception):
         pd.ulysses_seq_to_heads(torch.zeros(1, 3, 4, 2))
+
+
+def test_host_pipeline_head_groups():
+    """The host pipeline's groups cover the heads once, in order, never exceed the requested size and
+    shrink towards the end (the last group's kernels and copy back are the un-overlapped tail)."""
+    from paroatten_b200.host import head_groups
+    for H in (1, 2, 3, 5, 6, 7, 10, 12, 20, 40, 48):
+        for g in (None, 1, 2, 3, 4, 5, 8):
+            groups = head_groups(H, g)
+            sizes = [b - a for a, b in groups]
+            assert groups[0][0] == 0 and groups[-1][1] == H and sum(sizes) == H and min(sizes) > 0
+            assert all(groups[i][1] == groups[i + 1][0] for i in range(len(groups) - 1))
+            if g is not None:
+                assert max(sizes) <= g
+            tail = sizes[1:]
+            assert all(tail[i] >= tail[i + 1] for i in range(len(tail) - 1))
+    assert [b - a for a, b in head_groups(40)] == [5, 5, 5, 5, 5, 5, 4, 3, 2, 1]
+    assert len(head_groups(5)) >= 3
