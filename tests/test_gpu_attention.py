@@ -56,6 +56,31 @@ def test_kernel_on_oracle_quantised_operands(D, N, H, density, dtype):
     assert (lse.cpu() - want_lse).abs().max().item() < 2e-3
 
 
+@pytest.mark.parametrize("D,growth", [(128, 1.0), (64, 1.0), (128, -1.0), (128, 0.25)])
+def test_row_maximum_that_keeps_growing(D, growth):
+    """Keys of later blocks are scaled up (or down), so that along every row's list the running
+    maximum rises by more than the lazy-rescaling threshold again and again: the accumulator is
+    rescaled by the warp set whose step saw the rise, and the other set picks the new maximum up."""
+    B, H, N = 1, 2, 1024
+    q, k, v, _ = po.make_inputs(B, H, N, D, torch.bfloat16, seed=77)
+    nb = N // 64
+    j = torch.arange(nb, dtype=torch.float32)
+    f = (1.0 + growth * j) if growth > 0 else (1.0 + (-growth) * (nb - 1 - j))
+    k = (k.float() * f.repeat_interleave(64).reshape(1, 1, N, 1)).to(torch.bfloat16)
+    mask = po.make_mask(H, nb, 0.7, seed=5)
+    q8, qs, k8, ks, v8, vs, vm = quantised(q, k, v, [0] * H, (1, 1, N))
+    want, want_lse = po.sparse_attention(q8, qs, k8, ks, v8, vs, vm, mask, D ** -0.5, out_dtype=torch.bfloat16,
+                                         return_lse=True)
+    plan = pb.compact_plan(mask.to(DEV))
+    got, lse = pb.sparse_attn_quantized(q8.to(DEV), qs.to(DEV), k8.to(DEV), ks.to(DEV), v8.to(torch.float16).to(DEV),
+                                        vs.to(DEV), vm.to(DEV), plan, D ** -0.5, out_dtype=torch.bfloat16,
+                                        return_lse=True)
+    pb.check_status()
+    assert torch.isfinite(got.float()).all()
+    assert_close(got, want, f"D={D} growth={growth}")
+    assert ((lse.cpu() - want_lse).abs() / want_lse.abs().clamp_min(1.0)).max().item() < 2e-3
+
+
 def test_c1_plumbing_fixture():
     """BASELINE config 1 end to end against the committed oracle output."""
     cfg = po.CONFIGS["c1_plumbing"]
