@@ -37,6 +37,7 @@ enum {
 
 enum { PARO_F16 = 0, PARO_BF16 = 1 };
 enum { PARO_ROPE_NONE = 0, PARO_ROPE_REAL_F32 = 1, PARO_ROPE_COMPLEX_F64 = 2 };
+enum { PARO_NORM_NONE = 0, PARO_NORM_LAYER_HEAD = 1, PARO_NORM_RMS_ALL = 2 };
 
 int paro_version(void);
 const char* paro_last_error(void);
@@ -137,6 +138,36 @@ int paro_prep_v_fp8(const void* v, int dtype, int B, int H, int N, int D,
                     int smooth, float scale_max, uint8_t* v8, uint16_t* v16,
                     float* v_scale, float* vm, void* scratch, size_t scratch_bytes,
                     paro_stream_t stream);
+
+/* ---- Q/K normalisation folded into the passes above ----------------------------------------
+ * The processors call attn.norm_q / attn.norm_k between the projection and RoPE
+ * (cogvideox.py:161-164, wan.py:150-153; modules of the un-vendored diffusers package).  The
+ * *_norm entry points apply that normalisation to each row as it is read, before the rotation:
+ *   PARO_NORM_LAYER_HEAD  y = (x - mean) / sqrt(var + eps) * weight + bias over the D channels of one
+ *                         (token, head); weight, bias (nullable): [D] in the input dtype
+ *   PARO_NORM_RMS_ALL     y = dtype(dtype(x * inv_rms[b, token]) * weight[h*D + c]) with the statistic
+ *                         over all H*D channels of the token ("rms_norm_across_heads", wan.py:531);
+ *                         weight [H*D] in the input dtype, inv_rms [B,N] fp32 from paro_row_inv_rms
+ * Sums in fp64, all other operations separately rounded fp32, result rounded to the input dtype.
+ * All tokens are normalised (text tokens too).  The remaining arguments are those of
+ * paro_rope_permute / paro_prep_qk_int8; paro_prep_qk_int8_norm does not support smooth != 0. */
+int paro_row_inv_rms(const void* x, int dtype, int B, int H, int N, int D,
+                     int64_t stride_b, int64_t stride_h, int64_t stride_n,
+                     float eps, float* inv_rms, paro_stream_t stream);
+int paro_rope_permute_norm(const void* in, void* out, int dtype, int B, int H, int N, int D,
+                           int64_t stride_b, int64_t stride_h, int64_t stride_n,
+                           int n_text, int F, int Hh, int W, const int32_t* order_ids,
+                           int rope_mode, const void* cos_tab, const void* sin_tab,
+                           int pairs_f, int pairs_h,
+                           int norm_mode, const void* norm_weight, const void* norm_bias,
+                           const float* inv_rms, float eps, paro_stream_t stream);
+int paro_prep_qk_int8_norm(const void* x, int dtype, int B, int H, int N, int D,
+                           int64_t stride_b, int64_t stride_h, int64_t stride_n,
+                           int n_text, int F, int Hh, int W, const int32_t* order_ids,
+                           int rope_mode, const void* cos_tab, const void* sin_tab, int pairs_f, int pairs_h,
+                           int group, int8_t* out, float* scale,
+                           int norm_mode, const void* norm_weight, const void* norm_bias,
+                           const float* inv_rms, float eps, paro_stream_t stream);
 
 /* ---- sparse plan ----------------------------------------------------------------------- */
 

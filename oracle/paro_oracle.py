@@ -152,6 +152,62 @@ def apply_rope_complex(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, n_
     return out
 
 
+# --------------------------------------------------------------------------- QK normalisation
+# The processors normalise Q and K between the projection and RoPE (cogvideox.py:161-164,
+# wan.py:150-153) with modules of the third-party `diffusers` package, which is not vendored in the
+# reference and not pinned to a version: LayerNorm over the head dimension with affine parameters
+# for CogVideoX, RMSNorm over all heads' channels ("rms_norm_across_heads", wan.py:531) for Wan.
+# Parity unpinned: the arithmetic below is this project's definition (sums in fp64, every other
+# operation a separately rounded IEEE fp32 operation, result rounded to the input dtype), not a
+# transcript of that package.
+def _sqrt_f32(t: torch.Tensor) -> torch.Tensor:
+    """Correctly rounded fp32 square root.  torch's vectorised CPU sqrt is off by one unit in the last
+    place for a fraction of a percent of inputs; the fp64 root rounded to fp32 is exact (53 >= 2*24+2)."""
+    return torch.sqrt(t.double()).float()
+
+
+def layer_norm_heads(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], eps: float) -> torch.Tensor:
+    """x [..., D] -> (x - mean) * rstd * weight + bias over the last dimension."""
+    xd = x.double()
+    D = x.shape[-1]
+    mean = (xd.sum(-1, keepdim=True) / D).float()
+    dev = xd - mean.double()
+    var = ((dev * dev).sum(-1, keepdim=True) / D).float()
+    rstd = 1.0 / _sqrt_f32(var + torch.tensor(eps, dtype=torch.float32))
+    y = (x.float() - mean) * rstd
+    y = y * weight.float()
+    if bias is not None:
+        y = y + bias.float()
+    return y.to(x.dtype)
+
+
+def row_inv_rms(x_bnc: torch.Tensor, eps: float) -> torch.Tensor:
+    """x [B, N, C] -> 1/sqrt(mean(x^2) + eps) per token, fp32 [B, N]."""
+    xd = x_bnc.double()
+    ms = ((xd * xd).sum(-1) / x_bnc.shape[-1]).float()
+    return 1.0 / _sqrt_f32(ms + torch.tensor(eps, dtype=torch.float32))
+
+
+def rms_norm_across_heads(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """x [B, H, N, D], weight [H*D]: y = dtype(dtype(x * inv_rms[token]) * weight), the statistic taken
+    over all H*D channels of a token."""
+    B, H, N, D = x.shape
+    inv = row_inv_rms(x.permute(0, 2, 1, 3).reshape(B, N, H * D), eps)          # [B, N]
+    y = (x.float() * inv.reshape(B, 1, N, 1)).to(x.dtype)
+    return (y.float() * weight.float().reshape(1, H, 1, D)).to(x.dtype)
+
+
+def apply_qk_norm(x: torch.Tensor, norm) -> torch.Tensor:
+    """norm = None | ("layer", weight [D], bias [D] or None, eps) | ("rms", weight [H*D], eps)."""
+    if norm is None:
+        return x
+    if norm[0] == "layer":
+        return layer_norm_heads(x, norm[1], norm[2], norm[3])
+    if norm[0] == "rms":
+        return rms_norm_across_heads(x, norm[1], norm[2])
+    raise ValueError(f"unknown norm kind {norm[0]!r}")
+
+
 # --------------------------------------------------------------------------- quantisers
 def channel_mean(x: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
     """Mean over tokens of [B,H,N,D] -> [B,H,D].  The reference takes `k.mean(dim=-2)` in the
@@ -297,14 +353,15 @@ def sparse_attention(q_i8, q_scale, k_i8, k_scale, v8, v_scale, vm, mask, sm_sca
 
 
 def paro_attention(q, k, v, order_ids, mask, grid, n_text=0, rope=None, sm_scale=None,
-                   smooth_k=True, smooth_v=True, q_group=32, return_lse=False):
+                   smooth_k=True, smooth_v=True, q_group=32, return_lse=False, q_norm=None, k_norm=None):
     """The composed path as the processors run it (cogvideox.py:167-227): RoPE on Q,K ->
     permute Q,K,V -> INT8 Q (per 32 rows), INT8 K (per 64 rows, mean-smoothed), FP8 V ->
     block-sparse attention -> inverse permute.  `rope` = None | ("real"|"complex", cos, sin)
-    with per-token tables [F*H*W, D/2]."""
+    with per-token tables [F*H*W, D/2]; q_norm / k_norm as in `apply_qk_norm` (applied first)."""
     D = q.shape[-1]
     if sm_scale is None:
         sm_scale = D ** -0.5
+    q, k = apply_qk_norm(q, q_norm), apply_qk_norm(k, k_norm)
     if rope is not None:
         kind, cos, sin = rope
         fn = apply_rope_real if kind == "real" else apply_rope_complex

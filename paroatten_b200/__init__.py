@@ -7,12 +7,12 @@ from .plan import CompactPlan, PermutePlan, PlanStore, SparsePlan, compact_plan,
 from .processors import PARO_CogVideoXAttnProcessor2_0, PARO_WanAttnProcessor2_0, TimestepCallback
 from .quant import (channel_mean, per_block_int8, per_channel_fp8, per_warp_int8, prep_qk_int8, prep_v_fp8,
                     sub_mean)
-from .rope import RopeTables, rope_permutation, rope_permute, rope_tables
+from .rope import QKNorm, RopeTables, rope_permutation, rope_permute, rope_tables
 
 __all__ = [
     "paroattn", "paroattn_qk_int8_pv_fp16_cuda", "paro_attention", "sparse_attn_quantized", "check_status",
     "PARO_CogVideoXAttnProcessor2_0", "PARO_WanAttnProcessor2_0", "TimestepCallback",
     "per_block_int8", "per_warp_int8", "sub_mean", "per_channel_fp8", "channel_mean", "prep_qk_int8", "prep_v_fp8",
-    "rope_permutation", "rope_permute", "rope_tables", "RopeTables",
+    "rope_permutation", "rope_permute", "rope_tables", "RopeTables", "QKNorm",
     "HostPipelinedAttention", "CompactPlan", "SparsePlan", "PlanStore", "PermutePlan", "compact_plan", "perm_index",
 ]

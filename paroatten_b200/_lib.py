@@ -21,6 +21,7 @@ NVCC_FLAGS = ("-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17",
 PARO_OK, PARO_EINVAL, PARO_ESHAPE, PARO_EALIGN, PARO_ETIMEOUT, PARO_ECUDA, PARO_ECAP = 0, -1, -2, -3, -4, -5, -6
 F16, BF16 = 0, 1
 ROPE_NONE, ROPE_REAL_F32, ROPE_COMPLEX_F64 = 0, 1, 2
+NORM_NONE, NORM_LAYER_HEAD, NORM_RMS_ALL = 0, 1, 2
 
 _lock = threading.Lock()
 _lib = None
@@ -95,6 +96,11 @@ SIGNATURES = {
                                  _i32, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _sz, _vp]),
     "paro_prep_v_fp8": (_i32, [_vp, _i32, _i32, _i32, _i32, _i32, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _vp,
                                _i32, _f32, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "paro_row_inv_rms": (_i32, [_vp, _i32, _i32, _i32, _i32, _i32, _i64, _i64, _i64, _f32, _vp, _vp]),
+    "paro_rope_permute_norm": (_i32, [_vp, _vp, _i32, _i32, _i32, _i32, _i32, _i64, _i64, _i64, _i32, _i32, _i32, _i32,
+                                      _vp, _i32, _vp, _vp, _i32, _i32, _i32, _vp, _vp, _vp, _f32, _vp]),
+    "paro_prep_qk_int8_norm": (_i32, [_vp, _i32, _i32, _i32, _i32, _i32, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _vp,
+                                      _i32, _vp, _vp, _i32, _i32, _i32, _vp, _vp, _i32, _vp, _vp, _vp, _f32, _vp]),
     "paro_plan_count": (_i32, [_vp, _i32, _i32, _i32, _vp, _vp, _vp]),
     "paro_plan_fill": (_i32, [_vp, _i32, _i32, _i32, _vp, _vp, _i64, _vp, _vp, _i64, _vp]),
     "paro_sparse_attn": (_i32, [_vp, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _vp, _i32, _vp, _i32,

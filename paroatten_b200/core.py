@@ -168,9 +168,11 @@ def paroattn(q, k, v, tensor_layout: str = "HND", is_causal: bool = False, sm_sc
 def paro_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, permute_plan, sparse_plan, *,
                    i_block: int = 0, i_timestep: int = 0, grid_fhw: Tuple[int, int, int], n_text: int = 0,
                    rope: Optional[RopeTables] = None, tensor_layout: str = "HND", sm_scale: Optional[float] = None,
-                   smooth_k: bool = True, smooth_v: bool = True, return_lse: bool = False):
+                   smooth_k: bool = True, smooth_v: bool = True, return_lse: bool = False,
+                   q_norm=None, k_norm=None):
     """The whole path of one self-attention layer, as the reference processors compose it
-    (cogvideox.py:167-227): q, k, v in NATURAL token order ->
+    (cogvideox.py:161-227): q, k, v in NATURAL token order ->
+    [q_norm / k_norm (rope.QKNorm): the processors' norm_q / norm_k, applied to every token as it is read]
     RoPE on the video tokens of q, k + per-head F/H/W reordering of q, k, v (one fused pass each)
     -> INT8 q (per 32 rows) / INT8 k (per 64 rows, mean-smoothed) / FP8 v
     -> block-sparse attention over the kept blocks of sparse_plan[i_timestep, i_block]
@@ -184,6 +186,8 @@ def paro_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, permute_pl
         raise ValueError("q, k, v must share dtype fp16 or bf16")
     grid = tuple(int(g) for g in grid_fhw)
     (q, k, v), head_dim_og = _pad_head_dim(q, k, v)
+    if (q_norm is not None or k_norm is not None) and q.shape[-1] != head_dim_og:
+        raise ValueError("q_norm / k_norm need a head dimension of 64 or 128 (no padding)")
     if sm_scale is None:
         sm_scale = head_dim_og ** -0.5
     dev = q.device
@@ -205,12 +209,13 @@ def paro_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, permute_pl
         # Q and V: the quantisers read the natural-order tensors through the RoPE + reordering front end
         # (no reordered 16-bit copy).  Smoothed K needs the mean of the rotated values first; rotating
         # twice costs more than writing the rotated copy once, so K keeps the two-step form.
-        q8, qs, _ = prep_qk_int8(q, orders, grid, n_text, rope, group=32, tensor_layout=tensor_layout)
+        q8, qs, _ = prep_qk_int8(q, orders, grid, n_text, rope, group=32, tensor_layout=tensor_layout, norm=q_norm)
         if smooth_k:
-            kp = rope_permute(k, orders, grid, n_text, rope, tensor_layout=tensor_layout)
+            kp = rope_permute(k, orders, grid, n_text, rope, tensor_layout=tensor_layout, norm=k_norm)
             k8, ks = _quant_int8(kp, "HND", 64, km=channel_mean(kp))
         else:
-            k8, ks, _ = prep_qk_int8(k, orders, grid, n_text, rope, group=64, tensor_layout=tensor_layout)
+            k8, ks, _ = prep_qk_int8(k, orders, grid, n_text, rope, group=64, tensor_layout=tensor_layout,
+                                     norm=k_norm)
         v16, vs, vm, _ = prep_v_fp8(v, orders, grid, n_text, smooth_v=smooth_v, tensor_layout=tensor_layout)
         res = sparse_attn_quantized(q8, qs, k8, ks, v16, vs, vm, plan, sm_scale, out_dtype=q.dtype, q_group=32,
                                     inv_index=index, n_text=n_text, return_lse=return_lse, out_layout=tensor_layout)

@@ -7,6 +7,7 @@
 #include <type_traits>
 
 #include "common.cuh"
+#include "norm.cuh"
 #include "perm.cuh"
 #include "rope.cuh"
 
@@ -164,11 +165,11 @@ __global__ void channel_finalize_kernel(const ChannelPartial* __restrict__ part,
 
 // ---------------------------------------------------------------------------------------------
 // INT8: CTA = 128 threads = one 64-token block; warp w owns tokens 16w..16w+15.
-template <typename T, int D, int GROUP, int GM>
-__global__ void __launch_bounds__(128, GM == GM_ROPE_F64 ? 4 : (GM == GM_ROPE_F32 ? 5 : 6))
+template <typename T, int D, int GROUP, int GM, int NM>
+__global__ void __launch_bounds__(128, GM == GM_ROPE_F64 ? 4 : (GM == GM_ROPE_F32 || NM != PARO_NORM_NONE ? 5 : 6))
 quant_int8_kernel(const T* __restrict__ x, const T* __restrict__ km, int8_t* __restrict__ out,
                   float* __restrict__ scale, int H, int N, int64_t sb, int64_t sh, int64_t sn,
-                  float fold, int n_scale_per_bh, const Gather gather) {
+                  float fold, int n_scale_per_bh, const Gather gather, const NormArgs norm) {
   constexpr int TPR = D / 8;          // threads per token row
   constexpr int RPL = 32 / TPR;       // rows covered by one warp-wide load
   constexpr int LOADS = 16 / RPL;     // loads per thread
@@ -218,6 +219,11 @@ quant_int8_kernel(const T* __restrict__ x, const T* __restrict__ km, int8_t* __r
 #pragma unroll
   for (int i = 0; i < LOADS; ++i) {
     const int tok = tok0 + i * RPL;
+    if constexpr (NM != PARO_NORM_NONE) {   // all lanes: the row statistics are reduced with full-warp shuffles
+      int src = tok < N ? tok : 0;
+      if constexpr (GM != GM_PLAIN) src = __shfl_sync(0xffffffffu, d_src, i * RPL + lane / TPR);
+      normalize8<T, NM, TPR>(row[i], c8, D, b, h, N, src, norm);
+    }
     if constexpr (GM == GM_ROPE_F32 || GM == GM_ROPE_F64) {
       const int from = i * RPL + lane / TPR;
       const int gf = __shfl_sync(0xffffffffu, d_f, from);
@@ -388,20 +394,32 @@ extern "C" int paro_channel_mean(const void* x, int dtype, int B, int H, int N, 
 }
 
 namespace {
-template <typename T, int D>
-int launch_int8(const void* x, const void* km, int8_t* out, float* scale, int B, int H, int N, int64_t sb,
-                int64_t sh, int64_t sn, float fold, int group, cudaStream_t s, const Gather& g = Gather{}) {
+template <typename T, int D, int NM>
+void launch_int8_norm(const void* x, const void* km, int8_t* out, float* scale, int B, int H, int N, int64_t sb,
+                      int64_t sh, int64_t sn, float fold, int group, cudaStream_t s, const Gather& g, const NormArgs& nm) {
   const int nb = (N + 63) / 64;
   dim3 grid(nb, B * H);
   dispatch_gather(g, [&](auto gm) {
     constexpr int GM = decltype(gm)::value;
     if (group == 64)
-      quant_int8_kernel<T, D, 64, GM><<<grid, 128, 0, s>>>((const T*)x, (const T*)km, out, scale, H, N, sb, sh, sn, fold,
-                                                           nb, g);
+      quant_int8_kernel<T, D, 64, GM, NM><<<grid, 128, 0, s>>>((const T*)x, (const T*)km, out, scale, H, N, sb, sh, sn,
+                                                               fold, nb, g, nm);
     else
-      quant_int8_kernel<T, D, 32, GM><<<grid, 128, 0, s>>>((const T*)x, (const T*)km, out, scale, H, N, sb, sh, sn, fold,
-                                                           nb * 2, g);
+      quant_int8_kernel<T, D, 32, GM, NM><<<grid, 128, 0, s>>>((const T*)x, (const T*)km, out, scale, H, N, sb, sh, sn,
+                                                               fold, nb * 2, g, nm);
   });
+}
+
+template <typename T, int D>
+int launch_int8(const void* x, const void* km, int8_t* out, float* scale, int B, int H, int N, int64_t sb,
+                int64_t sh, int64_t sn, float fold, int group, cudaStream_t s, const Gather& g = Gather{},
+                const NormArgs& nm = NormArgs{}) {
+  if (nm.mode == PARO_NORM_LAYER_HEAD)
+    launch_int8_norm<T, D, PARO_NORM_LAYER_HEAD>(x, km, out, scale, B, H, N, sb, sh, sn, fold, group, s, g, nm);
+  else if (nm.mode == PARO_NORM_RMS_ALL)
+    launch_int8_norm<T, D, PARO_NORM_RMS_ALL>(x, km, out, scale, B, H, N, sb, sh, sn, fold, group, s, g, nm);
+  else
+    launch_int8_norm<T, D, PARO_NORM_NONE>(x, km, out, scale, B, H, N, sb, sh, sn, fold, group, s, g, nm);
   return check_launch("quant_int8_kernel");
 }
 }  // namespace
@@ -607,6 +625,30 @@ extern "C" int paro_prep_qk_int8(const void* x, int dtype, int B, int H, int N, 
   return dtype == PARO_F16
              ? run_prep_int8<__half>(x, B, H, N, D, stride_b, stride_h, stride_n, g, group, smooth, km_out, out, scale, scratch, s)
              : run_prep_int8<__nv_bfloat16>(x, B, H, N, D, stride_b, stride_h, stride_n, g, group, smooth, km_out, out, scale, scratch, s);
+}
+
+extern "C" int paro_prep_qk_int8_norm(const void* x, int dtype, int B, int H, int N, int D,
+                                      int64_t stride_b, int64_t stride_h, int64_t stride_n,
+                                      int n_text, int F, int Hh, int W, const int32_t* order_ids,
+                                      int rope_mode, const void* cos_tab, const void* sin_tab, int pairs_f, int pairs_h,
+                                      int group, int8_t* out, float* scale,
+                                      int norm_mode, const void* norm_weight, const void* norm_bias,
+                                      const float* inv_rms, float eps, paro_stream_t stream) {
+  if (int rc = check_tensor("paro_prep_qk_int8_norm(x)", x, dtype, B, H, N, D, stride_b, stride_h, stride_n)) return rc;
+  PARO_REQUIRE(group == 32 || group == 64, PARO_EINVAL, "paro_prep_qk_int8_norm: group must be 32 or 64, got %d", group);
+  PARO_REQUIRE(out && scale && aligned16(out), PARO_EINVAL, "paro_prep_qk_int8_norm: null or unaligned output");
+  Gather g{};
+  if (int rc = make_gather(&g, "paro_prep_qk_int8_norm", N, D, n_text, F, Hh, W, order_ids, rope_mode, cos_tab, sin_tab,
+                           pairs_f, pairs_h))
+    return rc;
+  if (int rc = check_norm("paro_prep_qk_int8_norm", norm_mode, norm_weight, norm_bias, inv_rms, eps)) return rc;
+  const NormArgs nm{norm_mode, norm_weight, norm_bias, inv_rms, eps};
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == PARO_F16)
+    return D == 128 ? launch_int8<__half, 128>(x, nullptr, out, scale, B, H, N, stride_b, stride_h, stride_n, 0.f, group, s, g, nm)
+                    : launch_int8<__half, 64>(x, nullptr, out, scale, B, H, N, stride_b, stride_h, stride_n, 0.f, group, s, g, nm);
+  return D == 128 ? launch_int8<__nv_bfloat16, 128>(x, nullptr, out, scale, B, H, N, stride_b, stride_h, stride_n, 0.f, group, s, g, nm)
+                  : launch_int8<__nv_bfloat16, 64>(x, nullptr, out, scale, B, H, N, stride_b, stride_h, stride_n, 0.f, group, s, g, nm);
 }
 
 extern "C" int paro_prep_v_fp8(const void* v, int dtype, int B, int H, int N, int D,

@@ -20,7 +20,7 @@ import torch
 from . import _lib
 from .core import paro_attention
 from .plan import PermutePlan, PlanStore, SparsePlan
-from .rope import RopeTables, rope_tables
+from .rope import QKNorm, RopeTables, rope_tables
 
 
 class _ProcessorBase:
@@ -35,6 +35,7 @@ class _ProcessorBase:
         self.i_block = 0
         self.i_timestep = 0
         self.smooth_k = True
+        self.fuse_qk_norm = True      # fold norm_q / norm_k into the RoPE + reorder + quantise passes
         self._rope_cache = {}
         self._pplan = None
         self._splan = None
@@ -61,7 +62,23 @@ class _ProcessorBase:
             self._rope_cache[key] = rope_tables(self.grid_fhw, head_dim, self.rope_family, device=device)
         return self._rope_cache[key]
 
-    def _attend(self, query, key, value, n_text, use_rope):
+    def _norms(self, attn, query, key, D, per_head):
+        """Folds attn.norm_q / attn.norm_k into the pre-attention passes when they are of a known
+        form (rope.QKNorm.from_module); any other module is simply called, as the reference does
+        (cogvideox.py:161-164, wan.py:150-153).  Returns (query, key, q_norm, k_norm)."""
+        out = []
+        for t, name in ((query, "norm_q"), (key, "norm_k")):
+            mod = getattr(attn, name, None)
+            spec = None
+            if mod is not None:
+                spec = QKNorm.from_module(mod, attn.heads, D) if self.fuse_qk_norm and D in (64, 128) else None
+                if spec is None:
+                    B, N, inner = t.shape
+                    t = mod(t.view(B, N, attn.heads, D)).reshape(B, N, inner) if per_head else mod(t)
+            out.append((t, spec))
+        return out[0][0], out[1][0], out[0][1], out[1][1]
+
+    def _attend(self, query, key, value, n_text, use_rope, q_norm=None, k_norm=None):
         """query/key/value: [B, N, H*D] projections; returns [B, N, H*D]."""
         B, N, inner = query.shape
         H = self._heads
@@ -73,7 +90,7 @@ class _ProcessorBase:
         out = paro_attention(q, k, v, pplan, splan, i_block=self.i_block, i_timestep=self.i_timestep,
                              grid_fhw=self.grid_fhw, n_text=n_text,
                              rope=self._rope(D, query.device) if use_rope else None,
-                             tensor_layout="NHD", smooth_k=self.smooth_k)
+                             tensor_layout="NHD", smooth_k=self.smooth_k, q_norm=q_norm, k_norm=k_norm)
         if isinstance(splan, PlanStore):     # stream the next layer's lists in while this layer computes
             splan.prefetch(self.i_timestep, self.i_block + 1)
         end.record()
@@ -108,11 +125,8 @@ class PARO_CogVideoXAttnProcessor2_0(_ProcessorBase):
         query, key, value = attn.to_q(hidden_states), attn.to_k(hidden_states), attn.to_v(hidden_states)
         B, N, inner = key.shape
         D = inner // attn.heads
-        if getattr(attn, "norm_q", None) is not None:
-            query = attn.norm_q(query.view(B, N, attn.heads, D)).reshape(B, N, inner)
-        if getattr(attn, "norm_k", None) is not None:
-            key = attn.norm_k(key.view(B, N, attn.heads, D)).reshape(B, N, inner)
-        hidden_states = self._attend(query, key, value, text_seq_length, image_rotary_emb is not None)
+        query, key, q_norm, k_norm = self._norms(attn, query, key, D, per_head=True)
+        hidden_states = self._attend(query, key, value, text_seq_length, image_rotary_emb is not None, q_norm, k_norm)
         hidden_states = attn.to_out[0](hidden_states)
         hidden_states = attn.to_out[1](hidden_states)
         encoder_hidden_states, hidden_states = hidden_states.split(
@@ -134,11 +148,9 @@ class PARO_WanAttnProcessor2_0(_ProcessorBase):
             raise ValueError("PARO_WanAttnProcessor2_0 handles self-attention only")
         self._heads = attn.heads
         query, key, value = attn.to_q(hidden_states), attn.to_k(hidden_states), attn.to_v(hidden_states)
-        if getattr(attn, "norm_q", None) is not None:
-            query = attn.norm_q(query)
-        if getattr(attn, "norm_k", None) is not None:
-            key = attn.norm_k(key)
-        hidden_states = self._attend(query, key, value, 0, rotary_emb is not None)
+        D = query.shape[-1] // attn.heads
+        query, key, q_norm, k_norm = self._norms(attn, query, key, D, per_head=False)
+        hidden_states = self._attend(query, key, value, 0, rotary_emb is not None, q_norm, k_norm)
         hidden_states = attn.to_out[0](hidden_states)
         hidden_states = attn.to_out[1](hidden_states)
         return hidden_states

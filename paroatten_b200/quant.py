@@ -128,11 +128,11 @@ def per_channel_fp8(v: torch.Tensor, tensor_layout: str = "HND", scale_max: floa
 
 
 def prep_qk_int8(x: torch.Tensor, order_ids: Optional[torch.Tensor], grid, n_text: int = 0, rope=None, group: int = 32,
-                 smooth: bool = False, tensor_layout: str = "HND"):
-    """RoPE + per-head reordering + INT8 quantisation of Q (group=32) or K (group=64, smooth=True for
-    mean smoothing) straight from the natural-order tensor: no reordered 16-bit copy is written.
-    Returns (int8 [B,H,N,D], scale, km or None), equal bit for bit to
-    per_warp_int8(rope_permute(x, ...))."""
+                 smooth: bool = False, tensor_layout: str = "HND", norm=None):
+    """[normalisation +] RoPE + per-head reordering + INT8 quantisation of Q (group=32) or K (group=64,
+    smooth=True for mean smoothing) straight from the natural-order tensor: no reordered 16-bit copy
+    is written.  Returns (int8 [B,H,N,D], scale, km or None), equal bit for bit to
+    per_warp_int8(rope_permute(x, ...)).  `norm` (a rope.QKNorm) cannot be combined with smooth."""
     _lib.require_cuda(x, order_ids)
     xv = _hnd(x, tensor_layout)
     B, H, N, D = xv.shape
@@ -146,6 +146,18 @@ def prep_qk_int8(x: torch.Tensor, order_ids: Optional[torch.Tensor], grid, n_tex
         km = torch.empty(B, H, D, dtype=x.dtype, device=x.device) if smooth else None
         scr = _stats_scratch(B, H, N, D, x.device) if smooth else None
         r = rope
+        if norm is not None:
+            if smooth:
+                raise ValueError("prep_qk_int8: norm and smooth cannot be combined (use rope_permute(norm=...) first)")
+            from .rope import _norm_call_args
+            mode, w, b, inv, eps, _keep = _norm_call_args(norm, xv)
+            _lib.check(_lib.lib().paro_prep_qk_int8_norm(
+                xv.data_ptr(), _lib.dtype_code(x.dtype), B, H, N, D, xv.stride(0), xv.stride(1), xv.stride(2),
+                int(n_text), F, Hh, W, _lib.ptr(order_ids), r.mode if r is not None else _lib.ROPE_NONE,
+                _lib.ptr(r.cos if r else None), _lib.ptr(r.sin if r else None), r.pairs_f if r else 0,
+                r.pairs_h if r else 0, int(group), out.data_ptr(), scale.data_ptr(),
+                mode, _lib.ptr(w), _lib.ptr(b), _lib.ptr(inv), eps, _lib.stream_ptr()))
+            return out, scale, None
         _lib.check(_lib.lib().paro_prep_qk_int8(
             xv.data_ptr(), _lib.dtype_code(x.dtype), B, H, N, D, xv.stride(0), xv.stride(1), xv.stride(2),
             int(n_text), F, Hh, W, _lib.ptr(order_ids), r.mode if r is not None else _lib.ROPE_NONE,

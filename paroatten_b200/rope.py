@@ -21,6 +21,56 @@ class RopeTables:
     pairs_h: int
 
 
+@dataclass
+class QKNorm:
+    """The normalisation the processors apply to Q or K between the projection and RoPE
+    (paroattention/cogvideox.py:161-164, wan.py:150-153), folded into the pre-attention passes.
+    kind "layer": LayerNorm over the head dimension, weight/bias [D];
+    kind "rms":   RMSNorm over all heads' channels of a token, weight [H*D], no bias.
+    Parameters are cast to the activations' dtype when used."""
+    kind: str
+    weight: torch.Tensor
+    bias: Optional[torch.Tensor] = None
+    eps: float = 1e-6
+
+    @classmethod
+    def from_module(cls, mod, heads: int, head_dim: int) -> Optional["QKNorm"]:
+        """QKNorm for a torch.nn.LayerNorm over head_dim or an RMS-norm module over heads*head_dim
+        (anything with a 1-D `weight` of that size, an `eps` and no bias); None if `mod` is neither."""
+        w = getattr(mod, "weight", None)
+        eps = getattr(mod, "eps", None)
+        if w is None or eps is None or w.dim() != 1:
+            return None
+        if isinstance(mod, torch.nn.LayerNorm) and w.numel() == head_dim:
+            return cls("layer", w.detach(), None if mod.bias is None else mod.bias.detach(), float(eps))
+        if "rms" in type(mod).__name__.lower() and w.numel() == heads * head_dim and getattr(mod, "bias", None) is None:
+            return cls("rms", w.detach(), None, float(eps))
+        return None
+
+
+def _norm_call_args(norm: Optional[QKNorm], xv: torch.Tensor):
+    """(mode, weight, bias, inv_rms, eps, keep-alive list) for an entry point that takes a norm;
+    xv is the [B,H,N,D] view of the activations.  For "rms" the per-token statistic is computed here."""
+    if norm is None:
+        return _lib.NORM_NONE, None, None, None, 0.0, []
+    B, H, N, D = xv.shape
+    w = norm.weight.to(device=xv.device, dtype=xv.dtype).contiguous()
+    if norm.kind == "layer":
+        if w.numel() != D:
+            raise ValueError("layer norm weight must have head_dim entries")
+        b = None if norm.bias is None else norm.bias.to(device=xv.device, dtype=xv.dtype).contiguous()
+        return _lib.NORM_LAYER_HEAD, w, b, None, float(norm.eps), [w, b]
+    if norm.kind == "rms":
+        if w.numel() != H * D:
+            raise ValueError("rms norm weight must have heads*head_dim entries")
+        inv = torch.empty(B, N, dtype=torch.float32, device=xv.device)
+        _lib.check(_lib.lib().paro_row_inv_rms(
+            xv.data_ptr(), _lib.dtype_code(xv.dtype), B, H, N, D, xv.stride(0), xv.stride(1), xv.stride(2),
+            float(norm.eps), inv.data_ptr(), _lib.stream_ptr()))
+        return _lib.NORM_RMS_ALL, w, None, inv, float(norm.eps), [w, inv]
+    raise ValueError(f"unknown norm kind {norm.kind!r}")
+
+
 def axis_pairs(head_dim: int, family: str) -> Tuple[int, int, int]:
     """Channel pairs rotated by the f / h / w coordinate: CogVideoX D/4, 3D/8, 3D/8 channels;
     Wan h = w = 2*(D//6) channels, the rest for f (paroattention/wan.py:492-493)."""
@@ -57,11 +107,11 @@ def rope_tables(grid, head_dim: int, family: str, theta: float = 10000.0, device
 
 def rope_permute(x: torch.Tensor, order_ids: Optional[torch.Tensor], grid, n_text: int = 0,
                  rope: Optional[RopeTables] = None, inverse: bool = False,
-                 tensor_layout: str = "HND") -> torch.Tensor:
-    """One pass over x ([B,H,N,D], or [B,N,H,D] when tensor_layout="NHD"): optional RoPE on the
-    video tokens, then head h's tokens gathered in its axis order (`order_ids` int32 [H] on the
-    GPU; None = keep the order).  inverse=True undoes the permutation (no RoPE).
-    Returns a new contiguous [B,H,N,D] tensor."""
+                 tensor_layout: str = "HND", norm: Optional[QKNorm] = None) -> torch.Tensor:
+    """One pass over x ([B,H,N,D], or [B,N,H,D] when tensor_layout="NHD"): optional normalisation
+    of every token (`norm`), optional RoPE on the video tokens, then head h's tokens gathered in its
+    axis order (`order_ids` int32 [H] on the GPU; None = keep the order).  inverse=True undoes the
+    permutation (no RoPE, no norm).  Returns a new contiguous [B,H,N,D] tensor."""
     _lib.require_cuda(x, order_ids)
     if tensor_layout == "NHD":
         x = x.transpose(1, 2)
@@ -78,6 +128,16 @@ def rope_permute(x: torch.Tensor, order_ids: Optional[torch.Tensor], grid, n_tex
     with torch.cuda.device(x.device):
         out = torch.empty(B, H, N, D, dtype=x.dtype, device=x.device)
         r = rope
+        if norm is not None:
+            if inverse:
+                raise ValueError("the inverse permutation does not normalise")
+            mode, w, b, inv, eps, _keep = _norm_call_args(norm, x)
+            _lib.check(_lib.lib().paro_rope_permute_norm(
+                x.data_ptr(), out.data_ptr(), _lib.dtype_code(x.dtype), B, H, N, D, x.stride(0), x.stride(1), x.stride(2),
+                int(n_text), F, Hh, W, _lib.ptr(order_ids), r.mode if r is not None else _lib.ROPE_NONE,
+                _lib.ptr(r.cos if r else None), _lib.ptr(r.sin if r else None), r.pairs_f if r else 0,
+                r.pairs_h if r else 0, mode, _lib.ptr(w), _lib.ptr(b), _lib.ptr(inv), eps, _lib.stream_ptr()))
+            return out
         _lib.check(_lib.lib().paro_rope_permute(
             x.data_ptr(), out.data_ptr(), _lib.dtype_code(x.dtype), B, H, N, D, x.stride(0), x.stride(1), x.stride(2),
             int(n_text), F, Hh, W, _lib.ptr(order_ids), int(bool(inverse)),

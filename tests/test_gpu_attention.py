@@ -216,6 +216,74 @@ def test_processors_on_a_stand_in_attention_module():
     assert torch.nn.functional.cosine_similarity(out.float().flatten(), ref.float().flatten(), dim=0) > 0.99
 
 
+def test_processors_fold_qk_norm():
+    """norm_q / norm_k of the two known forms are folded into the pre-attention passes; the result
+    agrees with calling the modules (the reference's order of operations) within the attention
+    tolerance, and the composed call with norms matches the oracle."""
+    import torch.nn as nn
+
+    class RMSNorm(nn.Module):   # stand-in with the attribute shape of an across-heads RMS norm
+        def __init__(self, dim, eps=1e-6):
+            super().__init__()
+            self.weight, self.eps, self.bias = nn.Parameter(torch.ones(dim)), eps, None
+
+        def forward(self, x):
+            v = x.float().pow(2).mean(-1, keepdim=True)
+            return (x.float() * torch.rsqrt(v + self.eps)).to(x.dtype) * self.weight
+
+    class Attn(nn.Module):
+        def __init__(self, dim, heads, kind):
+            super().__init__()
+            self.heads = heads
+            self.to_q, self.to_k, self.to_v = (nn.Linear(dim, dim) for _ in range(3))
+            self.to_out = nn.ModuleList([nn.Linear(dim, dim), nn.Dropout(0.0)])
+            mk = (lambda: nn.LayerNorm(dim // heads, eps=1e-6)) if kind == "layer" else (lambda: RMSNorm(dim))
+            self.norm_q, self.norm_k = mk(), mk()
+
+    torch.manual_seed(1)
+    heads, D = 2, 64
+    for kind, proc, grid, n_text in (("layer", pb.PARO_CogVideoXAttnProcessor2_0(), (2, 4, 8), 32),
+                                     ("rms", pb.PARO_WanAttnProcessor2_0(), (2, 4, 12), 0)):
+        attn = Attn(heads * D, heads, kind).to(DEV, torch.bfloat16)
+        with torch.no_grad():
+            for m in (attn.norm_q, attn.norm_k):
+                m.weight.add_(0.2 * torch.randn_like(m.weight))
+        n_img = grid[0] * grid[1] * grid[2]
+        nb = (n_text + n_img + 63) // 64
+        proc.grid_fhw = grid
+        proc.permute_plan = {"permute": torch.tensor([[4, 2]])}
+        proc.sparse_mask = torch.ones(1, 1, heads, nb, nb, dtype=torch.bool, device=DEV)
+        hs = torch.randn(1, n_img, heads * D, device=DEV, dtype=torch.bfloat16)
+        enc = torch.randn(1, n_text, heads * D, device=DEV, dtype=torch.bfloat16)
+        outs = []
+        for fuse in (True, False):
+            proc.fuse_qk_norm = fuse
+            with torch.no_grad():
+                o = proc(attn, hs, enc, image_rotary_emb=None) if kind == "layer" else proc(attn, hs, rotary_emb=None)
+            outs.append(torch.cat([o[1], o[0]], 1) if kind == "layer" else o)
+        pb.check_status()
+        cos = torch.nn.functional.cosine_similarity(outs[0].float().flatten(), outs[1].float().flatten(), dim=0)
+        assert cos > 0.999, (kind, cos)
+        assert pb.QKNorm.from_module(attn.norm_q, heads, D).kind == kind
+    assert pb.QKNorm.from_module(nn.Identity(), heads, D) is None
+
+    # composed call against the oracle
+    B, H, D, grid, n_text = 1, 2, 128, (2, 6, 10), 8
+    N = n_text + grid[0] * grid[1] * grid[2]
+    q, k, v, orders = po.make_inputs(B, H, N, D, torch.bfloat16, seed=31)
+    mask = po.make_mask(H, (N + 63) // 64, 0.7, seed=31)
+    g = torch.Generator().manual_seed(2)
+    wq, wk = ((1 + 0.2 * torch.randn(H * D, generator=g)).to(torch.bfloat16) for _ in range(2))
+    cos_t, sin_t = po.rope_full_tables(grid, D, "wan")
+    want = po.paro_attention(q, k, v, orders, mask, grid, n_text, rope=("complex", cos_t, sin_t),
+                             q_norm=("rms", wq, 1e-6), k_norm=("rms", wk, 1e-6))
+    got = pb.paro_attention(q.to(DEV), k.to(DEV), v.to(DEV), torch.tensor(orders), mask.to(DEV), grid_fhw=grid,
+                            n_text=n_text, rope=pb.rope_tables(grid, D, "wan"),
+                            q_norm=pb.QKNorm("rms", wq.to(DEV), None, 1e-6), k_norm=pb.QKNorm("rms", wk.to(DEV), None, 1e-6))
+    pb.check_status()
+    assert_close(got, want, "composed path with rms norms")
+
+
 def test_host_pipelined_matches_device_call():
     """Pinned host tensors through the head-group pipeline give bit-identical results."""
     B, H, D, grid, n_text = 2, 6, 64, (2, 6, 10), 8

@@ -193,3 +193,62 @@ def test_fused_prep_equals_separate_passes(dtype, D, family, grid, n_text):
     # NHD input, no fp8 copy
     v16b, _, _, none8 = pb.prep_v_fp8(v.transpose(1, 2).contiguous().to(DEV), ids, grid, n_text, tensor_layout="NHD")
     assert none8 is None and torch.equal(v16b, v16)
+
+
+def _norm_case(kind, H, D, dtype, seed):
+    g = torch.Generator().manual_seed(seed)
+    if kind == "layer":
+        w = (1.0 + 0.2 * torch.randn(D, generator=g)).to(dtype)
+        b = (0.1 * torch.randn(D, generator=g)).to(dtype)
+        return pb.QKNorm("layer", w.to(DEV), b.to(DEV), 1e-6), ("layer", w, b, 1e-6)
+    w = (1.0 + 0.2 * torch.randn(H * D, generator=g)).to(dtype)
+    return pb.QKNorm("rms", w.to(DEV), None, 1e-6), ("rms", w, 1e-6)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("kind,D,family,grid,n_text", [("layer", 64, "cogvideox", (3, 6, 10), 17),
+                                                       ("layer", 128, "wan", (2, 5, 9), 0),
+                                                       ("rms", 128, "wan", (3, 7, 11), 0),
+                                                       ("rms", 64, "cogvideox", (2, 5, 9), 40)])
+def test_qk_norm_folded_into_the_passes(kind, D, family, grid, n_text, dtype):
+    """norm_q / norm_k applied inside the RoPE + reorder (+ quantise) passes: the same bytes as the
+    oracle's normalise -> rotate -> reorder -> quantise, text tokens included."""
+    B, H = 2, 6
+    N = n_text + grid[0] * grid[1] * grid[2]
+    x = rand((B, H, N, D), dtype, 51, offset=0.3) * 3.0
+    orders = [(h * 5 + 3) % 6 for h in range(H)]
+    ids = torch.tensor(orders, dtype=torch.int32, device=DEV)
+    norm, onorm = _norm_case(kind, H, D, dtype, 52)
+    tabs = pb.rope_tables(grid, D, family)
+    cos, sin = po.rope_full_tables(grid, D, family)
+    fn = po.apply_rope_real if family == "cogvideox" else po.apply_rope_complex
+    xn = po.apply_qk_norm(x, onorm)
+    want = po.permute_tokens(fn(xn, cos, sin, n_text), orders, grid, n_text)
+    got = pb.rope_permute(x.to(DEV), ids, grid, n_text, tabs, norm=norm)
+    assert torch.equal(got.cpu(), want)
+    # norm only (no rotation, no reordering) and NHD input
+    assert torch.equal(pb.rope_permute(x.to(DEV), None, grid, n_text, norm=norm).cpu(), xn)
+    nhd = x.transpose(1, 2).contiguous().to(DEV)
+    assert torch.equal(pb.rope_permute(nhd, ids, grid, n_text, tabs, tensor_layout="NHD", norm=norm).cpu(), want)
+    # fused with the INT8 quantiser
+    for group in (32, 64):
+        w8, ws = po.quant_int8(want, group)
+        q8, qs, _ = pb.prep_qk_int8(x.to(DEV), ids, grid, n_text, tabs, group=group, norm=norm)
+        assert torch.equal(q8.cpu(), w8) and torch.equal(qs.cpu(), ws)
+    q8n, qsn, _ = pb.prep_qk_int8(nhd, ids, grid, n_text, tabs, group=32, tensor_layout="NHD", norm=norm)
+    w8, ws = po.quant_int8(want, 32)
+    assert torch.equal(q8n.cpu(), w8) and torch.equal(qsn.cpu(), ws)
+    with pytest.raises(ValueError):
+        pb.prep_qk_int8(x.to(DEV), ids, grid, n_text, tabs, group=64, smooth=True, norm=norm)
+
+
+def test_qk_norm_argument_errors():
+    x = torch.zeros(1, 2, 64, 64, dtype=torch.float16, device=DEV)
+    with pytest.raises(ValueError):
+        pb.rope_permute(x, None, (1, 8, 8), norm=pb.QKNorm("layer", torch.ones(32, device=DEV)))
+    with pytest.raises(ValueError):
+        pb.rope_permute(x, None, (1, 8, 8), norm=pb.QKNorm("rms", torch.ones(64, device=DEV)))
+    with pytest.raises(ValueError):
+        pb.rope_permute(x, None, (1, 8, 8), norm=pb.QKNorm("batch", torch.ones(64, device=DEV)))
+    with pytest.raises(ValueError):
+        pb.rope_permute(x, None, (1, 8, 8), inverse=True, norm=pb.QKNorm("layer", torch.ones(64, device=DEV)))

@@ -172,3 +172,29 @@ def test_c1_fixture():
     out = po.paro_attention(q, k, v, orders, mask, cfg["grid"])
     gold = torch.from_numpy(np.load(os.path.join(GOLD, "c1_plumbing_out.npz"))["out"]).view(torch.float16)
     assert torch.equal(out, gold)
+
+
+def test_qk_norm_restatement_against_torch():
+    """The oracle's normalisations agree with torch's own fp32 formulas up to the rounding of the
+    16-bit result (their arithmetic is this project's definition; the diffusers modules the
+    processors call are not available to pin them)."""
+    torch.manual_seed(3)
+    x = (torch.randn(2, 3, 50, 64) * 2 + 0.5).bfloat16()
+    w, b = (1 + 0.1 * torch.randn(64)).bfloat16(), (0.1 * torch.randn(64)).bfloat16()
+    y = po.layer_norm_heads(x, w, b, 1e-6)
+    ref = torch.nn.functional.layer_norm(x.float(), (64,), w.float(), b.float(), 1e-6)
+    assert y.dtype == x.dtype and (y.float() - ref).abs().max() <= 2 ** -7 * ref.abs().max()
+    w2 = (1 + 0.1 * torch.randn(192)).bfloat16()
+    y2 = po.rms_norm_across_heads(x, w2, 1e-6)
+    xf = x.float().permute(0, 2, 1, 3).reshape(2, 50, 192)
+    ref2 = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-6) * w2.float()).reshape(2, 50, 3, 64).permute(0, 2, 1, 3)
+    assert (y2.float() - ref2).abs().max() <= 2 ** -6 * ref2.abs().max()
+    assert po.apply_qk_norm(x, None) is x
+    # the composed oracle takes the norms first
+    q, k, v, orders = po.make_inputs(1, 2, 128, 64, torch.float16, seed=4)
+    mask = po.make_mask(2, 2, 1.0, seed=0)
+    wn = torch.ones(64, dtype=torch.float16)
+    a = po.paro_attention(q, k, v, orders, mask, (2, 8, 8), q_norm=("layer", wn, None, 1e-6), k_norm=("layer", wn, None, 1e-6))
+    b2 = po.paro_attention(po.layer_norm_heads(q, wn, None, 1e-6), po.layer_norm_heads(k, wn, None, 1e-6), v, orders, mask,
+                           (2, 8, 8))
+    assert torch.equal(a, b2)
