@@ -213,10 +213,9 @@ def main():
     plan = pb.compact_plan(mask_all[h0:h1].to(dev))
     pplan = pb.PermutePlan({"permute": orders.reshape(1, -1)}, wl["grid"], dev)
     rope = pb.rope_tables(wl["grid"], D, wl["family"], device=dev)
-    cnt = (plan.row_ptr[1:] - plan.row_ptr[:-1]).reshape(plan.slices, nb)
-    if nb % 2:
-        cnt = torch.cat([cnt, torch.zeros(plan.slices, 1, dtype=cnt.dtype, device=dev)], dim=1)
-    steps_local = int(cnt.reshape(plan.slices, -1, 2).amax(dim=-1).sum().item()) * B   # lock-step walk length
+    steps_local = plan.steps * B            # steps of the kernel's walk (one or two MMA groups each)
+    tiles_local = plan.tiles * B            # K/V tiles loaded = MMA groups of each kind issued
+    shared_local = plan.shared_tiles * B    # tiles that serve both q-blocks of their pair
     kept_local = plan.kept_blocks * B
     kept_total = int(mask_all.sum()) * B
     flops_block = 4 * 64 * 64 * D
@@ -306,7 +305,8 @@ def main():
         "config": {"workload": args.workload, "B": B, "H": H, "D": D, "N": N, "grid_fhw": list(wl["grid"]),
                    "n_text": n_text, "block": 64, "nominal_density": wl["density"],
                    "measured_density": kept_total / (B * H * nb * nb), "kept_blocks": kept_total,
-                   "lockstep_steps_rank0": steps_local, "partition": f"{world} x heads", "in_dtype": "bf16",
+                   "walk_steps_rank0": steps_local, "tiles_rank0": tiles_local,
+                   "shared_tiles_rank0": shared_local, "partition": f"{world} x heads", "in_dtype": "bf16",
                    "l2": "inputs larger than L2 (no flush needed)"},
         "attention_kernel_ms": attn_ms_max,
         "pre_attention_ms": ms_per_step - attn_ms_max,

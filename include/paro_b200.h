@@ -184,6 +184,17 @@ int paro_plan_fill(const uint8_t* mask, int slices, int nbq, int nbk,
                    const int32_t* pair_ptr, int32_t* pair_ent, int64_t pair_cap,
                    paro_stream_t stream);
 
+/* Walk order of the attention kernel, one schedule per pair of adjacent q-blocks (2p, 2p+1), built
+ * from the merged lists of paro_plan_fill: first the k-blocks both q-blocks keep (ascending; one
+ * K/V tile and one full-height MMA serve both), then the r-th block only 2p keeps beside the r-th
+ * block only 2p+1 keeps.  sched [size of pair_ent], entries of pair r from offset pair_ptr[r]:
+ * kbA | kbB << 16, 0xFFFF = no tile for that q-block in this step (needs nbk < 65535);
+ * sched_cnt [2 * slices*ceil(nbq/2)]: steps of q-block 2p, steps of q-block 2p+1 (each contiguous
+ * from step 0).  No counterpart in the reference (it tests one mask byte per block in the loop,
+ * qk_int_sv_f16_cuda_sm80.cu:268). */
+int paro_plan_schedule(const int32_t* pair_ptr, const int32_t* pair_ent, int slices, int nbq, int nbk,
+                       uint32_t* sched, int32_t* sched_cnt, paro_stream_t stream);
+
 /* ---- attention ------------------------------------------------------------------------- */
 
 /* Block-sparse attention over the kept 64x64 blocks with the inverse permutation fused
@@ -192,8 +203,8 @@ int paro_plan_fill(const uint8_t* mask, int slices, int nbq, int nbk,
  * permute_attn_out (cogvideox.py:64-110).
  *   q8,k8: contiguous int8 [B,H,N,D]; q_scale [B,H,ceil(N/64)*(64/q_group)], k_scale
  *   [B,H,ceil(N/64)]; v16: fp16 [B,H,D,ceil64(N)] (e4m3 values), v_scale/vm [B,H,D] (vm may
- *   be NULL); row_ptr/cols from paro_plan_* (per q-block ascending kept k-blocks), plan_slices = H
- *   (shared by the batch) or B*H;
+ *   be NULL); pair_ptr from paro_plan_count, sched/sched_cnt from paro_plan_schedule (the walk
+ *   order per pair of q-blocks), plan_slices = H (shared by the batch) or B*H;
  *   inv_idx (nullable): table of paro_build_perm_index -- output row n_text+j of head h is
  *   stored at token n_text+inv_idx[h][j]; out: [B,H,N,D] through element strides; lse
  *   (nullable) fp32 [B,H,N] in output token order, natural log; status: int32[4] device
@@ -203,7 +214,8 @@ int paro_plan_fill(const uint8_t* mask, int slices, int nbq, int nbk,
 int paro_sparse_attn(const int8_t* q8, const int8_t* k8, const uint16_t* v16,
                      const float* q_scale, int q_group, const float* k_scale,
                      const float* v_scale, const float* vm,
-                     const int32_t* row_ptr, const int32_t* cols, int plan_slices,
+                     const int32_t* pair_ptr, const uint32_t* sched, const int32_t* sched_cnt,
+                     int plan_slices,
                      const int32_t* inv_idx, int n_text,
                      void* out, int out_dtype,
                      int64_t out_stride_b, int64_t out_stride_h, int64_t out_stride_n,

@@ -301,6 +301,35 @@ def pair_union_plan(mask: torch.Tensor):
 
 
 # --------------------------------------------------------------------------- attention
+def pair_schedule(mask: torch.Tensor):
+    """Walk order of the attention kernel for every pair of adjacent q-blocks (2p, 2p+1) of a mask
+    [slices, nbq, nbk]: first the k-blocks both keep (ascending), then the r-th block only 2p keeps
+    beside the r-th block only 2p+1 keeps.  Returns (entries int32 in the slots of the pair's merged
+    list -- kbA | kbB << 16 with 0xFFFF for "none", unused slots all ones -- and counts int32
+    [slices*npairs, 2] = steps of q-block 2p, of 2p+1)."""
+    m = mask.reshape(-1, mask.shape[-2], mask.shape[-1]).bool()
+    slices, nbq, nbk = m.shape
+    npairs = (nbq + 1) // 2
+    ent, cnt = [], []
+    for sl in range(slices):
+        for p in range(npairs):
+            a = m[sl, 2 * p]
+            b = m[sl, 2 * p + 1] if 2 * p + 1 < nbq else torch.zeros(nbk, dtype=torch.bool)
+            both = torch.nonzero(a & b).flatten().tolist()
+            only_a = torch.nonzero(a & ~b).flatten().tolist()
+            only_b = torch.nonzero(b & ~a).flatten().tolist()
+            union = int((a | b).sum())
+            steps = [(k, k) for k in both]
+            for r in range(max(len(only_a), len(only_b))):
+                steps.append((only_a[r] if r < len(only_a) else 0xFFFF, only_b[r] if r < len(only_b) else 0xFFFF))
+            words = [ka | (kb << 16) for ka, kb in steps] + [0xFFFFFFFF] * (union - len(steps))
+            ent.extend(words)
+            cnt.append((len(both) + len(only_a), len(both) + len(only_b)))
+    e = torch.tensor(ent, dtype=torch.int64)
+    e = torch.where(e >= 2 ** 31, e - 2 ** 32, e).to(torch.int32)
+    return e, torch.tensor(cnt, dtype=torch.int32).reshape(-1, 2)
+
+
 def sparse_attention(q_i8, q_scale, k_i8, k_scale, v8, v_scale, vm, mask, sm_scale: float,
                      q_group: int = 32, out_dtype=torch.bfloat16, return_lse: bool = False,
                      heads: Optional[Sequence[int]] = None, q_blocks: Optional[Sequence[int]] = None):

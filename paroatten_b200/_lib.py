@@ -103,7 +103,8 @@ SIGNATURES = {
                                       _i32, _vp, _vp, _i32, _i32, _i32, _vp, _vp, _i32, _vp, _vp, _vp, _f32, _vp]),
     "paro_plan_count": (_i32, [_vp, _i32, _i32, _i32, _vp, _vp, _vp]),
     "paro_plan_fill": (_i32, [_vp, _i32, _i32, _i32, _vp, _vp, _i64, _vp, _vp, _i64, _vp]),
-    "paro_sparse_attn": (_i32, [_vp, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _vp, _i32, _vp, _i32,
+    "paro_plan_schedule": (_i32, [_vp, _vp, _i32, _i32, _i32, _vp, _vp, _vp]),
+    "paro_sparse_attn": (_i32, [_vp, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _vp, _i32, _vp, _i32,
                                 _i64, _i64, _i64, _vp, _i32, _i32, _i32, _i32, _f32, _vp, _vp]),
     "paro_status_poll": (_i32, [_vp, _vp, _vp]),
 }

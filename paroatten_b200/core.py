@@ -79,7 +79,8 @@ def sparse_attn_quantized(q_int8, q_scale, k_int8, k_scale, v_f16, v_scale, vm, 
             ev[0].record()
         _lib.check(_lib.lib().paro_sparse_attn(
             q_int8.data_ptr(), k_int8.data_ptr(), v_f16.data_ptr(), q_scale.data_ptr(), int(q_group),
-            k_scale.data_ptr(), v_scale.data_ptr(), _lib.ptr(vm), plan.row_ptr.data_ptr(), plan.cols.data_ptr(),
+            k_scale.data_ptr(), v_scale.data_ptr(), _lib.ptr(vm), plan.pair_ptr.data_ptr(), plan.sched.data_ptr(),
+            plan.sched_cnt.data_ptr(),
             plan.slices, _lib.ptr(inv_index), int(n_text), out.data_ptr(), _lib.dtype_code(out.dtype),
             ov.stride(0), ov.stride(1), ov.stride(2), _lib.ptr(lse), B, H, N, D, float(sm_scale),
             _status_words(dev).data_ptr(), _lib.stream_ptr()))

@@ -91,6 +91,51 @@ __global__ void plan_fill_kernel(const uint8_t* __restrict__ mask, int slices, i
   }
 }
 
+// Schedule of one pair of adjacent q-blocks, built from its merged list (ascending kb*4 + flags):
+// first the k-blocks BOTH q-blocks keep, in ascending order -- one tile then serves all 128 rows --
+// then the r-th block only q-block 2p keeps side by side with the r-th block only q-block 2p+1
+// keeps.  Entry i = kbA | kbB << 16 (0xFFFF = this q-block has no tile in step i); both q-blocks'
+// steps are contiguous from 0.  One warp per pair; the pair's entries live at the offsets of its
+// merged list (a schedule is never longer than the merged list), unused slots keep 0xFFFFFFFF.
+__global__ void plan_schedule_kernel(const int32_t* __restrict__ pair_ptr, const int32_t* __restrict__ pair_ent,
+                                     int prows, uint32_t* __restrict__ sched, int32_t* __restrict__ cnt) {
+  const int lane = threadIdx.x & 31;
+  const int warps = (gridDim.x * blockDim.x) >> 5;
+  uint16_t* sched16 = reinterpret_cast<uint16_t*>(sched);
+  for (int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < prows; r += warps) {
+    const int e0 = pair_ptr[r], e1 = pair_ptr[r + 1];
+    for (int e = e0 + lane; e < e1; e += 32) sched[e] = 0xFFFFFFFFu;
+    __syncwarp();
+    int ns = 0;
+    for (int e = e0; e < e1; e += 32) {
+      const int v = e + lane < e1 ? pair_ent[e + lane] : 0;
+      ns += __popc(__ballot_sync(0xffffffffu, (v & 3) == 3));
+    }
+    int c3 = 0, c1 = 0, c2 = 0;
+    for (int e = e0; e < e1; e += 32) {
+      const int v = e + lane < e1 ? pair_ent[e + lane] : 0;
+      const int f = v & 3, kb = v >> 2;
+      const uint32_t m3 = __ballot_sync(0xffffffffu, f == 3), m1 = __ballot_sync(0xffffffffu, f == 1),
+                     m2 = __ballot_sync(0xffffffffu, f == 2);
+      const uint32_t below = (1u << lane) - 1u;
+      if (f == 3) {
+        const int slot = c3 + __popc(m3 & below);
+        sched[e0 + slot] = (uint32_t)kb | ((uint32_t)kb << 16);
+      } else if (f == 1) {
+        sched16[2 * (size_t)(e0 + ns + c1 + __popc(m1 & below))] = (uint16_t)kb;
+      } else if (f == 2) {
+        sched16[2 * (size_t)(e0 + ns + c2 + __popc(m2 & below)) + 1] = (uint16_t)kb;
+      }
+      c3 += __popc(m3); c1 += __popc(m1); c2 += __popc(m2);
+    }
+    if (lane == 0) {
+      cnt[2 * r] = ns + c1;
+      cnt[2 * r + 1] = ns + c2;
+    }
+  }
+}
+
+
 }  // namespace paro
 
 using namespace paro;
@@ -139,4 +184,15 @@ extern "C" int paro_plan_fill(const uint8_t* mask, int slices, int nbq, int nbk,
     plan_fill_kernel<true><<<min(4096, (prow + 7) / 8), 256, 0, s>>>(mask, slices, nbq, nbk, npairs, pair_ptr,
                                                                      pair_ent, pair_cap);
   return check_launch("plan_fill", (cols_cap > 0) + (pair_cap > 0));
+}
+
+extern "C" int paro_plan_schedule(const int32_t* pair_ptr, const int32_t* pair_ent, int slices, int nbq, int nbk,
+                                  uint32_t* sched, int32_t* sched_cnt, paro_stream_t stream) {
+  PARO_REQUIRE(pair_ptr && sched_cnt, PARO_EINVAL, "paro_plan_schedule: null pointer");
+  PARO_REQUIRE(slices > 0 && nbq > 0, PARO_ESHAPE, "paro_plan_schedule: empty plan");
+  PARO_REQUIRE(nbk > 0 && nbk < 0xFFFF, PARO_ESHAPE, "paro_plan_schedule: nbk = %d does not fit 16 bits", nbk);
+  const int prow = slices * ((nbq + 1) / 2);
+  plan_schedule_kernel<<<min(4096, (prow + 7) / 8), 256, 0, (cudaStream_t)stream>>>(pair_ptr, pair_ent, prow, sched,
+                                                                                    sched_cnt);
+  return check_launch("plan_schedule_kernel");
 }

@@ -67,8 +67,9 @@ struct AttnParams {
   const float* k_scale;
   const float* v_scale;
   const float* vm;
-  const int32_t* row_ptr;
-  const int32_t* cols;
+  const int32_t* pair_ptr;
+  const uint32_t* sched;
+  const int32_t* sched_cnt;
   const int32_t* inv_idx;
   void* out;
   float* lse;
@@ -108,6 +109,12 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   float r;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
   return r;
+}
+// Global load that stays where it is written (the compiler may not sink it towards its use).
+__device__ __forceinline__ uint32_t ld_pinned_u32(const uint32_t* ptr) {
+  uint32_t v;
+  asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(v) : "l"(ptr));
+  return v;
 }
 __device__ __forceinline__ void named_barrier(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
@@ -175,14 +182,21 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int bh = blockIdx.x / p.npairs, pair = blockIdx.x % p.npairs;
   const int slice = bh % p.plan_slices;
-  // the two halves' lists (ascending kept k-blocks of q-blocks 2*pair and 2*pair+1)
-  const int row_a = slice * p.nb + 2 * pair;
-  const int a0 = p.row_ptr[row_a], n_a = p.row_ptr[row_a + 1] - a0;
-  const bool has_b = 2 * pair + 1 < p.nb;
-  const int b0 = has_b ? p.row_ptr[row_a + 1] : 0, n_b = has_b ? p.row_ptr[row_a + 2] - b0 : 0;
-  const int n_steps = max(n_a, n_b), n_min = min(n_a, n_b);
-  // position of half h's tile of step i in the order in which tiles pass through the rings
-  auto seq = [&](int i, int h) { return i < n_min ? 2 * i + h : 2 * n_min + (i - n_min); };
+  // The pair's schedule: entry i = kbA | kbB << 16 (0xFFFF: no tile for that half in step i).  First
+  // the k-blocks both halves keep (kbA == kbB: one K/V tile, one full-height MMA group), then the
+  // halves' remaining blocks side by side; each half's steps are contiguous from step 0.
+  const int prow = slice * p.npairs + pair;
+  const uint32_t* sched = p.sched + p.pair_ptr[prow];
+  const int n_a = p.sched_cnt[2 * prow], n_b = p.sched_cnt[2 * prow + 1];
+  const int n_steps = max(n_a, n_b);
+  // A step has one MMA group of each kind per tile: group 0 serves the upper half, or both halves
+  // when the tile is shared (kbA == kbB); group 1 serves the lower half.
+#define PARO_STEP_GROUPS(e)                                                        \
+  const int ka_ = (int)((e) & 0xFFFFu), kb_ = (int)((e) >> 16);                    \
+  const bool shared_ = ka_ == kb_;                                                 \
+  const bool act_[2] = {ka_ != 0xFFFF, !shared_ && kb_ != 0xFFFF};                 \
+  const int kblk_[2] = {ka_, kb_};                                                 \
+  const int which_[2] = {shared_ ? 2 : 0, 1};
 
   if (threadIdx.x == 0) {
     mbar_init(bar_q, 4);
@@ -220,36 +234,49 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
       // ---------------------------------------------------------------- TMA producer: K ring
       tma_prefetch_desc(&tm_k);
       bool ok = true;
+      int t = 0;   // tiles so far = position in the ring
+      // schedule entries are fetched two steps ahead of their use
+      uint32_t e_cur = n_steps > 0 ? sched[0] : 0u, e_nxt = n_steps > 1 ? sched[1] : 0u;
       for (int i = 0; i < n_steps && ok; ++i) {
-        for (int h = 0; h < 2; ++h) {
-          if (i >= (h ? n_b : n_a)) continue;
-          const int t = seq(i, h), st = t % KST, use = t / KST;
-          const int kb = p.cols[(h ? b0 : a0) + i];
+        PARO_STEP_GROUPS(e_cur)
+        e_cur = e_nxt;
+        if (i + 2 < n_steps) e_nxt = ld_pinned_u32(sched + i + 2);
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          if (!act_[j]) continue;
+          const int st = t % KST, use = t / KST;
+          ++t;
           if (use > 0 && !mbar_wait_bounded(bar_kfree + st, (use - 1) & 1, abort_flag, WAIT_LIMIT)) {
             report_timeout(p, abort_flag, 1, i);
             ok = false;
             break;
           }
           mbar_arrive_expect_tx(bar_kfull + st, Cfg::K_BYTES);
-          tma_load_3d(sK + st * Cfg::K_BYTES, &tm_k, 0, kb * 64, bh, bar_kfull + st);
+          tma_load_3d(sK + st * Cfg::K_BYTES, &tm_k, 0, kblk_[j] * 64, bh, bar_kfull + st);
         }
       }
     } else if (warp == 9 && lane == 0) {
       // ---------------------------------------------------------------- TMA producer: V ring
       tma_prefetch_desc(&tm_v);
       bool ok = true;
+      int t = 0;
+      uint32_t e_cur = n_steps > 0 ? sched[0] : 0u, e_nxt = n_steps > 1 ? sched[1] : 0u;
       for (int i = 0; i < n_steps && ok; ++i) {
-        for (int h = 0; h < 2; ++h) {
-          if (i >= (h ? n_b : n_a)) continue;
-          const int t = seq(i, h), st = t % VST, use = t / VST;
-          const int kb = p.cols[(h ? b0 : a0) + i];
+        PARO_STEP_GROUPS(e_cur)
+        e_cur = e_nxt;
+        if (i + 2 < n_steps) e_nxt = ld_pinned_u32(sched + i + 2);
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          if (!act_[j]) continue;
+          const int st = t % VST, use = t / VST;
+          ++t;
           if (use > 0 && !mbar_wait_bounded(bar_vfree + st, (use - 1) & 1, abort_flag, WAIT_LIMIT)) {
             report_timeout(p, abort_flag, 9, i);
             ok = false;
             break;
           }
           mbar_arrive_expect_tx(bar_vfull + st, Cfg::V_BYTES);
-          tma_load_3d(sV + st * Cfg::V_BYTES, &tm_v, kb * 64, 0, bh, bar_vfull + st);
+          tma_load_3d(sV + st * Cfg::V_BYTES, &tm_v, kblk_[j] * 64, 0, bh, bar_vfull + st);
         }
       }
     } else if (warp == 10 && lane == 0) {
@@ -260,25 +287,40 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
       do {
         ATT_WAIT(bar_q, 0, 2, -1)
         bool ok = true;
+        int t = 0;
+        uint32_t e_cur = n_steps > 0 ? sched[0] : 0u, e_nxt = n_steps > 1 ? sched[1] : 0u;
         for (int i = 0; i < n_steps && ok; ++i) {
-          for (int h = 0; h < 2; ++h) {   // one lane-masked MMA group per half that still has blocks
-            if (i >= (h ? n_b : n_a)) continue;
-            const int t = seq(i, h), st = t % KST;
-            // this half's scores of step i-1 are in registers, its rows of S may be overwritten
-            if ((i > 0 && !mbar_wait_bounded(bar_sfree + 2 * h + ((i - 1) & 1), ((i - 1) >> 1) & 1, abort_flag, WAIT_LIMIT)) ||
-                !mbar_wait_bounded(bar_kfull + st, (t / KST) & 1, abort_flag, WAIT_LIMIT)) {
+          PARO_STEP_GROUPS(e_cur)
+          e_cur = e_nxt;
+          if (i + 2 < n_steps) e_nxt = ld_pinned_u32(sched + i + 2);
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {   // one MMA group per tile; lane-masked unless it serves both halves
+            if (!act_[j]) continue;
+            const int w = which_[j], st = t % KST, use = t / KST;
+            ++t;
+            // the scores of step i-1 of the halves served are in registers: their rows of S may be overwritten
+            bool good = true;
+            if (i > 0) {
+              const int par = (i - 1) & 1, ph = ((i - 1) >> 1) & 1;
+              if (w != 1) good = good && mbar_wait_bounded(bar_sfree + par, ph, abort_flag, WAIT_LIMIT);
+              if (w != 0) good = good && mbar_wait_bounded(bar_sfree + 2 + par, ph, abort_flag, WAIT_LIMIT);
+            }
+            good = good && mbar_wait_bounded(bar_kfull + st, use & 1, abort_flag, WAIT_LIMIT);
+            if (!good) {
               report_timeout(p, abort_flag, 3, i);
               ok = false;
               break;
             }
             tc_fence_after();
             const uint64_t dK = smem_desc(smem_u32(sK + st * Cfg::K_BYTES), D);
-            const uint32_t lo = h ? 0xffffffffu : 0u, hi = ~lo;   // lanes NOT written: the other half's rows
+            // lanes NOT written: the rows of a half the tile does not serve
+            const uint32_t lo = w == 1 ? 0xffffffffu : 0u, hi = w == 0 ? 0xffffffffu : 0u;
 #pragma unroll
             for (int k = 0; k < D / 32; ++k)
               mma_i8_ts_masked(tS, tQ + 8 * k, desc_advance(dK, 32 * k), IDESC_QK, k > 0, lo, lo, hi, hi);
             mma_commit(bar_kfree + st);
-            mma_commit(bar_sready + 2 * h + (i & 1));
+            if (w != 1) mma_commit(bar_sready + (i & 1));
+            if (w != 0) mma_commit(bar_sready + 2 + (i & 1));
           }
         }
       } while (false);
@@ -286,25 +328,38 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
       // ---------------------------------------------------------------- MMA issuer: O += P.V
       constexpr uint32_t IDESC_PV = instr_desc(1, 0, 0, 128, D);   // f32 += f16 * f16
       bool ok = true;
+      int t = 0;
+      uint32_t e_cur = n_steps > 0 ? sched[0] : 0u, e_nxt = n_steps > 1 ? sched[1] : 0u;
       for (int i = 0; i < n_steps && ok; ++i) {
-        for (int h = 0; h < 2; ++h) {
-          if (i >= (h ? n_b : n_a)) continue;
-          const int t = seq(i, h), st = t % VST;
-          if (!mbar_wait_bounded(bar_pready + 2 * h + (i & 1), (i >> 1) & 1, abort_flag, WAIT_LIMIT) ||
-              !mbar_wait_bounded(bar_vfull + st, (t / VST) & 1, abort_flag, WAIT_LIMIT)) {
+        PARO_STEP_GROUPS(e_cur)
+        e_cur = e_nxt;
+        if (i + 2 < n_steps) e_nxt = ld_pinned_u32(sched + i + 2);
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          if (!act_[j]) continue;
+          const int w = which_[j], st = t % VST, use = t / VST;
+          ++t;
+          const int par = i & 1, ph = (i >> 1) & 1;
+          bool good = true;
+          if (w != 1) good = good && mbar_wait_bounded(bar_pready + par, ph, abort_flag, WAIT_LIMIT);
+          if (w != 0) good = good && mbar_wait_bounded(bar_pready + 2 + par, ph, abort_flag, WAIT_LIMIT);
+          good = good && mbar_wait_bounded(bar_vfull + st, use & 1, abort_flag, WAIT_LIMIT);
+          if (!good) {
             report_timeout(p, abort_flag, 5, i);
             ok = false;
             break;
           }
           tc_fence_after();
           const uint64_t dV = smem_desc(smem_u32(sV + st * Cfg::V_BYTES), 128);
-          const uint32_t lo = h ? 0xffffffffu : 0u, hi = ~lo;
+          const uint32_t lo = w == 1 ? 0xffffffffu : 0u, hi = w == 0 ? 0xffffffffu : 0u;
+          // both halves start at step 0, so a tile that serves both never mixes a first with a later step
 #pragma unroll
           for (int k = 0; k < 4; ++k)
             mma_f16_ts_masked(tO, tP + 8 * k, desc_advance(dV, 32 * k), IDESC_PV, (i > 0 || k > 0) ? 1u : 0u, lo, lo, hi,
                               hi);
           mma_commit(bar_vfree + st);
-          mma_commit(bar_pvdone + 2 * h + (i & 1));
+          if (w != 1) mma_commit(bar_pvdone + par);
+          if (w != 0) mma_commit(bar_pvdone + 2 + par);
         }
       }
     }
@@ -317,7 +372,7 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
     const int half = qd >> 1;                // which q-block of the pair
     const uint32_t lane_off = (uint32_t)(qd * 32) << 16;
     const int n_mine = half ? n_b : n_a;
-    const int32_t* my_cols = p.cols + (half ? b0 : a0);
+    auto my_kb = [&](int i) { return (int)((sched[i] >> (16 * half)) & 0xFFFFu); };   // this half's k-block of step i
     if (threadIdx.x < D) {
       s_vscale[threadIdx.x] = p.v_scale[(size_t)bh * D + threadIdx.x];
       s_vm[threadIdx.x] = p.vm ? p.vm[(size_t)bh * D + threadIdx.x] : 0.f;
@@ -356,13 +411,13 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
     uint64_t* const my_pready = bar_pready + 2 * half + set;
     uint64_t* const prev_pvdone = bar_pvdone + 2 * half + (set ^ 1);   // P.V of the steps of the other parity
     const float* kscale_bh = p.k_scale + (size_t)bh * p.nb;
-    int kb_next = set < n_mine ? my_cols[set] : 0;
+    int kb_next = set < n_mine ? my_kb(set) : 0;
     float ks_next = set < n_mine ? kscale_bh[kb_next] : 0.f;
     for (int i = set; i < n_mine; i += 2) {   // the two halves only meet in the issuers' queues
       const int kb = kb_next;
       const float kscale = ks_next;
       if (i + 2 < n_mine) {   // fetched one step ahead so that the loads are off the critical path
-        kb_next = my_cols[i + 2];
+        kb_next = my_kb(i + 2);
         ks_next = kscale_bh[kb_next];
       }
       ok = wait_bar(my_sready, i >> 1, 6, i);
@@ -592,13 +647,14 @@ using namespace paro;
 extern "C" int paro_sparse_attn(const int8_t* q8, const int8_t* k8, const uint16_t* v16,
                                 const float* q_scale, int q_group, const float* k_scale,
                                 const float* v_scale, const float* vm,
-                                const int32_t* row_ptr, const int32_t* cols, int plan_slices,
+                                const int32_t* pair_ptr, const uint32_t* sched, const int32_t* sched_cnt,
+                                int plan_slices,
                                 const int32_t* inv_idx, int n_text,
                                 void* out, int out_dtype,
                                 int64_t out_stride_b, int64_t out_stride_h, int64_t out_stride_n,
                                 float* lse, int B, int H, int N, int D, float sm_scale,
                                 int32_t* status, paro_stream_t stream) {
-  PARO_REQUIRE(q8 && k8 && v16 && q_scale && k_scale && v_scale && row_ptr && cols && out && status, PARO_EINVAL,
+  PARO_REQUIRE(q8 && k8 && v16 && q_scale && k_scale && v_scale && pair_ptr && sched && sched_cnt && out && status, PARO_EINVAL,
                "paro_sparse_attn: null pointer");
   PARO_REQUIRE(B > 0 && H > 0 && N > 0, PARO_ESHAPE, "paro_sparse_attn: empty problem");
   PARO_REQUIRE(D == 64 || D == 128, PARO_ESHAPE, "paro_sparse_attn: head_dim %d unsupported (64 or 128)", D);
@@ -614,7 +670,7 @@ extern "C" int paro_sparse_attn(const int8_t* q8, const int8_t* k8, const uint16
   PARO_REQUIRE(sm_scale > 0.f, PARO_EINVAL, "paro_sparse_attn: sm_scale must be positive");
   AttnParams p;
   p.q8 = q8; p.q_scale = q_scale; p.k_scale = k_scale; p.v_scale = v_scale; p.vm = vm;
-  p.row_ptr = row_ptr; p.cols = cols; p.inv_idx = inv_idx;
+  p.pair_ptr = pair_ptr; p.sched = sched; p.sched_cnt = sched_cnt; p.inv_idx = inv_idx;
   p.out = out; p.lse = lse; p.status = status;
   p.osb = out_stride_b; p.osh = out_stride_h; p.osn = out_stride_n;
   p.plan_slices = plan_slices; p.q_group = q_group; p.n_text = n_text;

@@ -38,12 +38,32 @@ class CompactPlan:
     slices: int
     nbq: int
     nbk: int
-    row_ptr: torch.Tensor    # int32 [slices*nbq + 1]
-    cols: torch.Tensor       # int32 [kept]: ascending k-block ids per q-block
-    pair_ptr: Optional[torch.Tensor]   # int32 [slices*ceil(nbq/2) + 1]
-    pair_ent: Optional[torch.Tensor]   # int32: kb*4 + flags per pair of adjacent q-blocks (merged walk; auxiliary)
+    row_ptr: Optional[torch.Tensor]    # int32 [slices*nbq + 1]                      (CSR form of the mask;
+    cols: Optional[torch.Tensor]       # int32 [kept]: ascending k-block ids per q-block   not read by the kernel)
+    pair_ptr: torch.Tensor             # int32 [slices*ceil(nbq/2) + 1]: offsets of a pair's merged list and schedule
+    pair_ent: Optional[torch.Tensor]   # int32: kb*4 + flags per pair of adjacent q-blocks (merged list; auxiliary)
     kept_blocks: int         # number of true entries of the mask
-    pair_tiles: int          # size of the merged (union) walk over all q-block pairs
+    pair_tiles: int          # size of the merged (union) lists over all q-block pairs
+    sched: Optional[torch.Tensor] = None       # int32 [pair_tiles]: kbA | kbB << 16 per step (what the kernel walks)
+    sched_cnt: Optional[torch.Tensor] = None   # int32 [slices*ceil(nbq/2), 2]: steps of q-block 2p and of 2p+1
+
+    @property
+    def steps(self) -> int:
+        """Steps of the kernel's walk over all pairs (a step is one or two MMA groups)."""
+        return int(self.sched_cnt.max(dim=1).values.sum().item())
+
+    @property
+    def tiles(self) -> int:
+        """K/V tiles the kernel loads = MMA groups of each kind it issues: a tile shared by both
+        q-blocks of a pair counts once."""
+        c = self.sched_cnt.long()
+        n = int(c.sum().item())
+        return n - self.shared_tiles
+
+    @property
+    def shared_tiles(self) -> int:
+        """Tiles that serve both q-blocks of their pair."""
+        return int((self.pair_ent & 3).eq(3).sum().item()) if self.pair_ent is not None else -1
 
 
 def compact_plan(mask: torch.Tensor) -> CompactPlan:
@@ -67,7 +87,12 @@ def compact_plan(mask: torch.Tensor) -> CompactPlan:
         pair_ent = torch.empty(max(tiles, 1), dtype=torch.int32, device=m.device)
         _lib.check(L.paro_plan_fill(m.data_ptr(), slices, nbq, nbk, row_ptr.data_ptr(), cols.data_ptr(), kept,
                                     pair_ptr.data_ptr(), pair_ent.data_ptr(), tiles, s))
-    return CompactPlan(slices, nbq, nbk, row_ptr, cols[:kept], pair_ptr, pair_ent[:tiles], kept, tiles)
+        sched = torch.empty(max(tiles, 1), dtype=torch.int32, device=m.device)
+        sched_cnt = torch.empty(slices * npairs, 2, dtype=torch.int32, device=m.device)
+        _lib.check(L.paro_plan_schedule(pair_ptr.data_ptr(), pair_ent.data_ptr(), slices, nbq, nbk, sched.data_ptr(),
+                                        sched_cnt.data_ptr(), s))
+    return CompactPlan(slices, nbq, nbk, row_ptr, cols[:kept], pair_ptr, pair_ent[:tiles], kept, tiles,
+                       sched[:tiles], sched_cnt)
 
 
 class SparsePlan:
@@ -124,8 +149,9 @@ class PlanStore:
 
     def __init__(self, sparse: Optional[torch.Tensor] = None, device=None, _lists=None):
         self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self.kept = {}
         if _lists is not None:
-            self.meta, self.lists = _lists
+            self.meta, self.lists, self.kept = _lists
         else:
             if sparse.dim() != 5:
                 raise ValueError("sparse plan must be [timestep_bins, layers, heads, nb, nb]")
@@ -135,12 +161,14 @@ class PlanStore:
             for t in range(T):
                 for l in range(L):
                     p = compact_plan(sparse[t, l].to(self.device))
-                    self.lists[(t, l)] = (p.row_ptr.cpu().pin_memory(), p.cols.cpu().pin_memory())
-        cap = max(c.numel() for _, c in self.lists.values())
-        rows = self.meta["H"] * self.meta["nbq"] + 1
+                    self.lists[(t, l)] = tuple(x.cpu().pin_memory() for x in (p.pair_ptr, p.sched, p.sched_cnt))
+                    self.kept[(t, l)] = p.kept_blocks
+        cap = max(c.numel() for _, c, _ in self.lists.values())
+        prows = self.meta["H"] * ((self.meta["nbq"] + 1) // 2)
         with torch.cuda.device(self.device):
-            self._buf = [(torch.empty(rows, dtype=torch.int32, device=self.device),
-                          torch.empty(max(cap, 1), dtype=torch.int32, device=self.device)) for _ in range(2)]
+            self._buf = [(torch.empty(prows + 1, dtype=torch.int32, device=self.device),
+                          torch.empty(max(cap, 1), dtype=torch.int32, device=self.device),
+                          torch.empty(prows, 2, dtype=torch.int32, device=self.device)) for _ in range(2)]
             self._stream = torch.cuda.Stream(self.device)
         self._slot = {}          # key -> (buffer index, event of its copy)
         self._next = 0
@@ -158,14 +186,15 @@ class PlanStore:
         b = self._next
         self._next ^= 1
         self._slot = {k: v for k, v in self._slot.items() if v[0] != b}
-        row_ptr, cols = self.lists[key]
+        pair_ptr, sched, sched_cnt = self.lists[key]
         with torch.cuda.device(self.device):
             fence = torch.cuda.Event()
             fence.record(torch.cuda.current_stream())
             self._stream.wait_event(fence)
             with torch.cuda.stream(self._stream):
-                self._buf[b][0].copy_(row_ptr, non_blocking=True)
-                self._buf[b][1][:cols.numel()].copy_(cols, non_blocking=True)
+                self._buf[b][0].copy_(pair_ptr, non_blocking=True)
+                self._buf[b][1][:sched.numel()].copy_(sched, non_blocking=True)
+                self._buf[b][2].copy_(sched_cnt, non_blocking=True)
                 ev = torch.cuda.Event()
                 ev.record(self._stream)
         self._slot[key] = (b, ev)
@@ -182,13 +211,17 @@ class PlanStore:
         with torch.cuda.device(self.device):
             torch.cuda.current_stream().wait_event(ev)
         m = self.meta
-        return CompactPlan(m["H"], m["nbq"], m["nbk"], self._buf[b][0], self._buf[b][1][:n], None, None, int(n), 0)
+        return CompactPlan(m["H"], m["nbq"], m["nbk"], None, None, self._buf[b][0], None, int(self.kept.get(key, 0)),
+                           int(n), self._buf[b][1][:n], self._buf[b][2])
 
     def save(self, path: str) -> None:
-        torch.save({"meta": self.meta, "lists": {f"{t},{l}": (r.clone(), c.clone()) for (t, l), (r, c) in self.lists.items()}}, path)
+        torch.save({"meta": self.meta, "kept": {f"{t},{l}": n for (t, l), n in self.kept.items()},
+                    "lists": {f"{t},{l}": tuple(x.clone() for x in v) for (t, l), v in self.lists.items()}}, path)
 
     @classmethod
     def load(cls, path: str, device=None) -> "PlanStore":
         blob = torch.load(path, map_location="cpu")
-        lists = {tuple(int(x) for x in k.split(",")): (r.pin_memory(), c.pin_memory()) for k, (r, c) in blob["lists"].items()}
-        return cls(device=device, _lists=(blob["meta"], lists))
+        key = lambda k: tuple(int(x) for x in k.split(","))
+        lists = {key(k): tuple(x.pin_memory() for x in v) for k, v in blob["lists"].items()}
+        kept = {key(k): int(n) for k, n in blob.get("kept", {}).items()}
+        return cls(device=device, _lists=(blob["meta"], lists, kept))

@@ -321,8 +321,9 @@ def test_plan_store_prefetch_and_roundtrip(tmp_path):
             for l in range(L):
                 st.prefetch(t, l + 1)
                 plan = st.get(t, l)
-                ptr, cols = po.compact_plan(sparse[t, l])
-                assert torch.equal(plan.row_ptr.cpu(), ptr) and torch.equal(plan.cols.cpu(), cols)
+                sched, cnt = po.pair_schedule(sparse[t, l])
+                assert torch.equal(plan.sched.cpu(), sched) and torch.equal(plan.sched_cnt.cpu(), cnt)
+                assert plan.kept_blocks == int(sparse[t, l].sum())
     N, D = nb * 64 - 20, 64
     q, k, v, orders = po.make_inputs(1, H, N, D, torch.float16, seed=4)
     args = dict(grid_fhw=(1, 1, N))

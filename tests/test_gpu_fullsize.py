@@ -49,6 +49,12 @@ def test_full_size_workload(name):
     assert bool(((d > 0) | row_start[1:]).all())
     flags = plan.pair_ent & 3
     assert int(((flags & 1) != 0).sum() + ((flags & 2) != 0).sum()) == plan.kept_blocks
+    # the kernel's schedule covers every kept block once: per pair, steps of 2p + steps of 2p+1 = its kept blocks
+    per_pair = torch.zeros(plan.slices * ((nb + 1) // 2), dtype=torch.int64, device=DEV)
+    rows = torch.arange(plan.slices * nb, device=DEV)
+    per_pair.index_add_(0, (rows // nb) * ((nb + 1) // 2) + (rows % nb) // 2, counts.to(DEV).long())
+    assert torch.equal(plan.sched_cnt.long().sum(1), per_pair)
+    assert plan.tiles + plan.shared_tiles == plan.kept_blocks and plan.steps <= plan.tiles
 
     # --- reordering: inverse(forward(x)) == x over the whole tensor, text rows untouched
     fwd = pb.rope_permute(v, ids, grid, n_text)

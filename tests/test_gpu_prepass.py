@@ -43,6 +43,12 @@ def test_compact_plan(slices, nb, density):
     assert torch.equal(plan.row_ptr.cpu(), ptr) and torch.equal(plan.cols.cpu(), cols)
     assert torch.equal(plan.pair_ptr.cpu(), pptr) and torch.equal(plan.pair_ent.cpu(), pent)
     assert plan.kept_blocks == int(mask.sum()) and plan.pair_tiles == pent.numel()
+    # the schedule the attention kernel walks: shared blocks first, then the rest side by side
+    sched, cnt = po.pair_schedule(mask)
+    assert torch.equal(plan.sched.cpu(), sched) and torch.equal(plan.sched_cnt.cpu(), cnt)
+    both = int((pent & 3).eq(3).sum())
+    assert plan.shared_tiles == both and plan.tiles == plan.kept_blocks - both
+    assert plan.steps == int(cnt.max(dim=1).values.sum())
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])

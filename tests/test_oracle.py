@@ -198,3 +198,28 @@ def test_qk_norm_restatement_against_torch():
     b2 = po.paro_attention(po.layer_norm_heads(q, wn, None, 1e-6), po.layer_norm_heads(k, wn, None, 1e-6), v, orders, mask,
                            (2, 8, 8))
     assert torch.equal(a, b2)
+
+
+def test_pair_schedule_covers_every_kept_block_once():
+    """Shared blocks first (one tile for both q-blocks), then the remaining blocks side by side; each
+    q-block's steps are contiguous from 0 and list exactly its kept blocks."""
+    for nb, density in ((1, 1.0), (5, 0.5), (8, 0.3), (9, 0.9), (6, 0.0)):
+        mask = torch.rand(3, nb, nb, generator=torch.Generator().manual_seed(nb)) < density
+        sched, cnt = po.pair_schedule(mask)
+        pptr, pent = po.pair_union_plan(mask)
+        assert sched.numel() == pent.numel() and cnt.shape == (3 * ((nb + 1) // 2), 2)
+        npairs = (nb + 1) // 2
+        for r in range(3 * npairs):
+            sl, p = divmod(r, npairs)
+            words = [w & 0xFFFFFFFF for w in sched[pptr[r]:pptr[r + 1]].tolist()]
+            na, nb_ = cnt[r].tolist()
+            a = [w & 0xFFFF for w in words[:na]]
+            b = [w >> 16 for w in words[:nb_]]
+            assert sorted(a) == mask[sl, 2 * p].nonzero().flatten().tolist()
+            want_b = mask[sl, 2 * p + 1].nonzero().flatten().tolist() if 2 * p + 1 < nb else []
+            assert sorted(b) == want_b
+            shared = [w for w in words if (w & 0xFFFF) == (w >> 16) and w != 0xFFFFFFFF]
+            assert words[:len(shared)] == shared                      # shared tiles come first
+            assert all(w == 0xFFFFFFFF for w in words[max(na, nb_):])  # unused slots
+            assert all((w & 0xFFFF) == 0xFFFF for w in words[na:max(na, nb_)])
+            assert all((w >> 16) == 0xFFFF for w in words[nb_:max(na, nb_)])
