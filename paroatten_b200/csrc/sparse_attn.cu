@@ -1,10 +1,11 @@
 // Block-sparse attention over kept 64x64 blocks for sm_100a.
 //
 // Work item (one CTA): a PAIR of adjacent 64-row q-blocks of one (batch, head), i.e. a 128-row
-// tile -- the native tcgen05.mma M.  The two halves walk their OWN lists of kept k-blocks in
-// lock step: in step i the upper half works on its i-th kept block and the lower half on its i-th
-// kept block.  Each MMA is issued with the query tile of all 128 rows but with a lane mask that
-// keeps it from writing the other half's accumulator rows, so both halves always have work (all
+// tile -- the native tcgen05.mma M.  The pair walks a schedule built with the plan: first the
+// k-blocks BOTH q-blocks keep (one K/V tile and one full-height MMA group serve all 128 rows), then
+// the remaining blocks of the upper half side by side with the remaining blocks of the lower half.
+// In a side-by-side step each MMA is issued with the query tile of all 128 rows but with a lane mask
+// that keeps it from writing the other half's accumulator rows, so both halves always have work (all
 // four SM sub-partitions run exponentials) and nothing is computed for blocks that are not kept.
 //
 //   warps 0-7   softmax + epilogue.  Row r of the tile belongs to two threads, one in each WARP SET:
