@@ -223,7 +223,10 @@ int paro_sparse_attn(const int8_t* q8, const int8_t* k8, const uint16_t* v16,
                      int32_t* status, paro_stream_t stream);
 
 /* Synchronises `stream`, copies the 4 status words to host_out (host pointer, may be NULL)
- * and returns PARO_OK, PARO_ETIMEOUT (word 0 non-zero) or PARO_ECUDA. */
+ * and returns PARO_OK, PARO_ETIMEOUT (word 0 non-zero) or PARO_ECUDA.  After a timeout word 1 names
+ * the waiter that gave up (1 K loader, 9 V loader, 2/3 score issuer, 5 P.V issuer, 6 softmax
+ * waiting for scores, 7/8 softmax waiting for P.V, 10 softmax waiting for the running maximum),
+ * word 2 the work item (block index) and word 3 its step. */
 int paro_status_poll(const int32_t* status, int32_t* host_out, paro_stream_t stream);
 
 #ifdef __cplusplus
