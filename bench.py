@@ -24,7 +24,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 WORKLOADS = {
-    # BASELINE.json configs[3], [2], [1]
+    # the reference's three model-shaped workloads
     "wan14b_720p": dict(B=1, H=40, D=128, grid=(21, 45, 80), n_text=0, density=0.2, family="wan", window=0),
     "wan1p3b_480p": dict(B=2, H=12, D=128, grid=(21, 30, 52), n_text=0, density=0.3, family="wan", window=1),
     "cogvideox_5b": dict(B=2, H=48, D=64, grid=(13, 30, 45), n_text=226, density=0.3, family="cogvideox", window=0),

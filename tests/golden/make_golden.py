@@ -1,6 +1,6 @@
 """Regenerates the fixtures in this directory.  Run from the repository root:
 
-    python tests/golden/make_golden.py [--reference /path/to/PAROAtten]
+    python tests/golden/make_golden.py --reference /path/to/PAROAtten
 
 Two kinds of fixture are written:
 
@@ -99,7 +99,7 @@ def reference_perm_tables(mod, grid, n_text):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of the reference project")
     args = ap.parse_args()
 
     if os.path.isdir(args.reference):

@@ -82,7 +82,7 @@ def test_row_maximum_that_keeps_growing(D, growth):
 
 
 def test_c1_plumbing_fixture():
-    """BASELINE config 1 end to end against the committed oracle output."""
+    """The small CPU-runnable configuration end to end against the committed oracle output."""
     cfg = po.CONFIGS["c1_plumbing"]
     N = 1024
     q, k, v, orders = po.make_inputs(cfg["B"], cfg["H"], N, cfg["D"], cfg["dtype"], seed=0)

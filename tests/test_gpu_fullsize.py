@@ -1,4 +1,4 @@
-"""The BASELINE workloads at their full sizes: size-independent properties over the whole result plus
+"""The model-shaped workloads at their full sizes: size-independent properties over the whole result plus
 spot checks of one head against the CPU oracle (whole-tensor oracle runs would take hours)."""
 import math
 
