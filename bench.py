@@ -270,8 +270,10 @@ def main():
     if not args.no_e2e:
         # the public host-memory entry point: head groups pipelined over three streams, so the copy of
         # group c+1 and the read-back of group c-1 overlap the kernels of group c
-        hq, hk, hv = (t_.cpu().pin_memory() for t_ in (q, k, v))
-        ho = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+        hq, hk, hv = (pb.pinned_like(t_.shape, t_.dtype, dev) for t_ in (q, k, v))   # pages next to the GPU
+        for h_, d_ in zip((hq, hk, hv), (q, k, v)):
+            h_.copy_(d_)
+        ho = pb.pinned_like(out.shape, out.dtype, dev)
         pipe = pb.HostPipelinedAttention(orders_all[h0:h1], mask_all[h0:h1], (B, Hl, N, D), torch.bfloat16,
                                          grid_fhw=wl["grid"], n_text=n_text, rope=rope,
                                          device=dev)

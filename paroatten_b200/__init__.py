@@ -2,7 +2,7 @@
 NVIDIA B200 (sm_100a), behind the reference's `paroattention` Python names."""
 from .core import (check_status, paro_attention, paroattn, paroattn_qk_int8_pv_fp16_cuda,
                    sparse_attn_quantized)
-from .host import HostPipelinedAttention
+from .host import HostPipelinedAttention, pinned_like
 from .plan import CompactPlan, PermutePlan, PlanStore, SparsePlan, compact_plan, perm_index
 from .processors import PARO_CogVideoXAttnProcessor2_0, PARO_WanAttnProcessor2_0, TimestepCallback
 from .quant import (channel_mean, per_block_int8, per_channel_fp8, per_warp_int8, prep_qk_int8, prep_v_fp8,
@@ -14,5 +14,5 @@ __all__ = [
     "PARO_CogVideoXAttnProcessor2_0", "PARO_WanAttnProcessor2_0", "TimestepCallback",
     "per_block_int8", "per_warp_int8", "sub_mean", "per_channel_fp8", "channel_mean", "prep_qk_int8", "prep_v_fp8",
     "rope_permutation", "rope_permute", "rope_tables", "RopeTables", "QKNorm",
-    "HostPipelinedAttention", "CompactPlan", "SparsePlan", "PlanStore", "PermutePlan", "compact_plan", "perm_index",
+    "HostPipelinedAttention", "pinned_like", "CompactPlan", "SparsePlan", "PlanStore", "PermutePlan", "compact_plan", "perm_index",
 ]

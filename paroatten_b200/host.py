@@ -18,6 +18,50 @@ from .plan import CompactPlan, PermutePlan, compact_plan
 from .rope import RopeTables
 
 
+def _gpu_local_cpus(device) -> Optional[set]:
+    """CPUs on the NUMA node the GPU's PCIe slot hangs off (from sysfs), or None when unknown."""
+    try:
+        pr = torch.cuda.get_device_properties(device)
+        path = f"/sys/bus/pci/devices/{pr.pci_domain_id:04x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0/local_cpulist"
+        with open(path) as f:
+            text = f.read().strip()
+        cpus = set()
+        for part in text.split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        return cpus or None
+    except Exception:
+        return None
+
+
+def pinned_like(shape, dtype, device=None) -> torch.Tensor:
+    """A pinned host tensor whose pages sit on the NUMA node next to the GPU: the calling thread is
+    bound to that node's CPUs while the buffer is allocated and first touched, then released again.
+    Copies from a far node cross the inter-socket link and lose PCIe bandwidth.  Falls back to a plain
+    pinned allocation when the topology cannot be read."""
+    import os
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    old = None
+    try:
+        cpus = _gpu_local_cpus(device)
+        if cpus:
+            old = os.sched_getaffinity(0)
+            usable = cpus & old
+            if usable:
+                os.sched_setaffinity(0, usable)
+            else:
+                old = None
+    except Exception:
+        old = None
+    try:
+        t = torch.empty(shape, dtype=dtype).pin_memory()
+        t.zero_()          # first touch
+    finally:
+        if old is not None:
+            os.sched_setaffinity(0, old)
+    return t
+
+
 def head_groups(H: int, heads_per_group: Optional[int] = None) -> List[Tuple[int, int]]:
     """Cuts H heads into the [h0, h1) groups the pipeline works on.  The host-to-device copies are
     the slowest stage, so what is left after the last copy -- the last group's kernels and its
@@ -79,7 +123,7 @@ class HostPipelinedAttention:
             if not t.is_pinned():
                 raise ValueError("q, k, v must be in pinned host memory (torch.Tensor.pin_memory())")
         if out is None:
-            out = torch.empty(self.shape, dtype=self.dtype).pin_memory()
+            out = pinned_like(self.shape, self.dtype, self.device)
         elif out.is_cuda or tuple(out.shape) != self.shape or not out.is_pinned():
             raise ValueError("out must be a pinned host tensor of the same shape")
         with torch.cuda.device(self.device):

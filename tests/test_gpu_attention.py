@@ -296,7 +296,10 @@ def test_host_pipelined_matches_device_call():
                              n_text=n_text, rope=tabs)
     pipe = pb.HostPipelinedAttention(orders, mask, (B, H, N, D), torch.bfloat16, grid_fhw=grid, n_text=n_text, rope=tabs,
                                      heads_per_group=4)
-    hq, hk, hv = (t.pin_memory() for t in (q, k, v))
+    hq, hk = (t.pin_memory() for t in (q, k))
+    hv = pb.pinned_like(v.shape, v.dtype)      # pinned pages allocated next to the GPU
+    hv.copy_(v)
+    assert hv.is_pinned() and not hv.is_cuda
     for _ in range(2):
         got = pipe(hq, hk, hv)
         torch.cuda.synchronize()
