@@ -39,6 +39,14 @@ def test_version_and_argument_errors_without_gpu():
     assert rc == _lib.PARO_EINVAL and b"group" in handle.paro_last_error()
     rc = handle.paro_rope_permute(addr, addr + 16, 1, 1, 1, 10, 64, 0, 0, 64, 0, 1, 2, 3, None, 0, 0, None, None, 0, 0, None)
     assert rc == _lib.PARO_ESHAPE and b"!= N" in handle.paro_last_error()
+    rc = handle.paro_plan_schedule(addr, addr, 1, 4, 70000, addr, addr, None)
+    assert rc == _lib.PARO_ESHAPE and b"16 bits" in handle.paro_last_error()
+    rc = handle.paro_rope_permute_norm(addr, addr + 16, 1, 1, 1, 6, 64, 0, 0, 64, 0, 1, 2, 3, None, 0, None, None, 0, 0,
+                                       7, None, None, None, 1e-6, None)
+    assert rc == _lib.PARO_EINVAL and b"norm_mode" in handle.paro_last_error()
+    rc = handle.paro_rope_permute_norm(addr, addr + 16, 1, 1, 1, 6, 64, 0, 0, 64, 0, 1, 2, 3, None, 0, None, None, 0, 0,
+                                       2, addr, None, None, 1e-6, None)
+    assert rc == _lib.PARO_EINVAL and b"inv_rms" in handle.paro_last_error()
     assert handle.paro_channel_stats_scratch_bytes(1, 2, 1000, 128) == 2 * 2 * 128 * 16 + 2 * 2 * 128 * 4
     with pytest.raises(ValueError):
         _lib.check(rc)
