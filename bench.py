@@ -140,6 +140,11 @@ def run_reference(args, wl_name, wl, rank):
     reference arm times the CPU restatement of its algorithm (the oracle) on the host cores."""
     if rank != 0:
         return
+    # all host cores this process may use (torchrun sets OMP_NUM_THREADS=1 for multi-rank launches)
+    try:
+        torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
+    except (AttributeError, OSError):
+        torch.set_num_threads(max(1, os.cpu_count() or 1))
     run, flops, desc = cpu_sample(wl)
     sec = time_cpu(run, args.steps, max(1, min(args.warmup, 3)))
     tops = flops / sec / 1e12
