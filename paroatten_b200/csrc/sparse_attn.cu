@@ -196,8 +196,8 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
   const int ka_ = (int)((e) & 0xFFFFu), kb_ = (int)((e) >> 16);                    \
   const bool shared_ = ka_ == kb_;                                                 \
   const bool act_[2] = {ka_ != 0xFFFF, !shared_ && kb_ != 0xFFFF};                 \
-  const int kblk_[2] = {ka_, kb_};                                                 \
-  const int which_[2] = {shared_ ? 2 : 0, 1};
+  [[maybe_unused]] const int kblk_[2] = {ka_, kb_};                                \
+  [[maybe_unused]] const int which_[2] = {shared_ ? 2 : 0, 1};
 
   if (threadIdx.x == 0) {
     mbar_init(bar_q, 4);
