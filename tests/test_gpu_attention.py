@@ -125,6 +125,20 @@ def test_composed_path(family, D, grid, n_text, dtype):
     assert torch.equal(got2.transpose(1, 2), got)
 
 
+def test_mask_per_batch_entry():
+    """A [B, H, nb, nb] mask gives every batch entry its own plan slices."""
+    B, H, N, D = 2, 3, 700, 64
+    q, k, v, _ = po.make_inputs(B, H, N, D, torch.bfloat16, seed=12)
+    nb = (N + 63) // 64
+    masks = torch.stack([po.make_mask(H, nb, 0.3, seed=40), po.make_mask(H, nb, 0.8, seed=41)])   # [B, H, nb, nb]
+    got = pb.paro_attention(q.to(DEV), k.to(DEV), v.to(DEV), torch.zeros(H, dtype=torch.int32), masks.to(DEV),
+                            grid_fhw=(1, 1, N))
+    pb.check_status()
+    for b in range(B):
+        want = po.paro_attention(q[b:b + 1], k[b:b + 1], v[b:b + 1], [0] * H, masks[b], (1, 1, N))
+        assert_close(got[b:b + 1], want, f"batch entry {b}")
+
+
 def test_reference_operator_signature():
     """paroattn_qk_int8_pv_fp16_cuda(q, k, v, sparse): already reordered inputs, bool mask."""
     B, H, N, D = 2, 3, 520, 96   # head_dim padded to 128 like the reference
