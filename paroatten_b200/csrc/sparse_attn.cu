@@ -194,10 +194,14 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
   const int n_a = p.sched_cnt[2 * prow], n_b = p.sched_cnt[2 * prow + 1];
   const int n_steps = max(n_a, n_b);
   // A step has one MMA group of each kind per tile: group 0 serves the upper half, or both halves
-  // when the tile is shared (kbA == kbB); group 1 serves the lower half.
+  // when the tile is shared (kbA == kbB); group 1 serves the lower half.  Sharing halves the tensor
+  // work of such a step but makes the two halves wait for each other in it; at D = 64 the tensor pipe
+  // is not what limits the kernel and the wait costs 13 % on the CogVideoX shape, so tiles are only
+  // shared at D = 128.
+  constexpr bool SHARE_TILES = (D == 128);
 #define PARO_STEP_GROUPS(e)                                                        \
   const int ka_ = (int)((e) & 0xFFFFu), kb_ = (int)((e) >> 16);                    \
-  const bool shared_ = ka_ == kb_;                                                 \
+  const bool shared_ = SHARE_TILES && ka_ == kb_;                                  \
   const bool act_[2] = {ka_ != 0xFFFF, !shared_ && kb_ != 0xFFFF};                 \
   [[maybe_unused]] const int kblk_[2] = {ka_, kb_};                                \
   [[maybe_unused]] const int which_[2] = {shared_ ? 2 : 0, 1};
