@@ -499,7 +499,8 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
         ok = wait_bar(prev_pvdone, (i - 1) >> 1, 7, i);
         if (!ok) break;
         const float alpha = resc ? ex2_approx(m_old - m_new) : 1.f;
-#pragma unroll
+        // (rare, and deliberately not unrolled: unrolled, this loop costs the hot path 19 spilled registers)
+#pragma unroll 1
         for (int c = 0; c < D / 16; ++c) {  // the thread whose step moved the maximum rescales the whole row
           uint32_t o[16];
           const uint32_t addr = tO + lane_off + (uint32_t)(16 * c);
