@@ -45,6 +45,7 @@ constexpr int ATT_THREADS = 384;
 constexpr int ATT_SOFTMAX_THREADS = 256;
 constexpr int TMEM_COLS = 256;
 constexpr long long WAIT_LIMIT = 400000000; // SM cycles (~0.2 s) before a wait gives up
+constexpr float SCORE_BIAS = 12582912.0f;   // 1.5 * 2^23, bit pattern 0x4B400000
 constexpr float RESCALE_TAU = 8.0f;         // rescale O only when the row max grows by > 2^8
 
 template <int D> struct AttnCfg {
@@ -440,9 +441,13 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(my_sfree);
-        // int32 scores -> fp32 (exact: |s| < 2^24)
+        // int32 scores -> fp32 by an integer addition instead of a conversion: the bit pattern
+        // 0x4B400000 + s is the float SCORE_BIAS + s exactly (|s| <= 127 * 127 * D < 2^22).  The bias is
+        // monotonic, so the row maximum is taken over the biased values, and it is folded into the
+        // constant of the multiply-add that forms the exponent; that constant is rounded once, to
+        // within 0.75 of one integer score step, common to the row and step.
 #pragma unroll
-        for (int j = 0; j < 64; ++j) f[j] = (float)(int)s[j];
+        for (int j = 0; j < 64; ++j) f[j] = __int_as_float((int)s[j] + 0x4B400000);
       }
       const int valid = min(64, p.N - kb * 64);   // columns inside the sequence
       if (valid < 64) {
@@ -461,7 +466,7 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
         }
       }
       const float sc = rowscale * kscale;
-      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sc;
+      const float mx = (fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) - SCORE_BIAS) * sc;
       // The running maximum of the row passes between the two threads that share it through shared
       // memory: step i reads what step i-1 (the other warp set) published.
       float m_old = -INFINITY;
@@ -512,7 +517,8 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
         }
         tmem_wait_st();
       }
-      const uint64_t sc2 = pack2(sc, sc), negm2 = pack2(-m_new, -m_new);
+      const float xoff = fmaf(-SCORE_BIAS, sc, -m_new);   // (bias + s) * sc + xoff = s * sc - m
+      const uint64_t sc2 = pack2(sc, sc), negm2 = pack2(xoff, xoff);
       uint64_t sum2[2] = {0ull, 0ull};
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
