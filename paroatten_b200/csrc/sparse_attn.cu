@@ -49,10 +49,9 @@ constexpr float SCORE_BIAS = 12582912.0f;   // 1.5 * 2^23, bit pattern 0x4B40000
 constexpr float RESCALE_TAU = 8.0f;         // rescale O only when the row max grows by > 2^8
 
 template <int D> struct AttnCfg {
-  // Ring depths.  TMEM allows two CTAs per SM; the rings are kept well below what shared memory would
-  // hold, because the loads run far ahead of their use anyway (depths from 2 to 6 give the same time
-  // within noise) while the shared memory left over becomes L1, which the schedule entries, the k-block
-  // scales and the register spills of the softmax warps live in: K3/V3 is 3 % faster than K5/V4.
+  // Ring depths.  TMEM allows two CTAs per SM; the loads run far ahead of their use at any depth from 2
+  // to 6 (same time within noise), so the rings are kept short and the shared memory left over is
+  // requested back as L1 (carve-out attribute at launch) for the schedule entries and k-block scales.
 #ifndef PARO_ATT_KST128
 #define PARO_ATT_KST128 3
 #define PARO_ATT_VST128 3
