@@ -323,10 +323,10 @@ def main():
                      "frac": achieved / peak_i8,
                      "peak_note": f"2 x bf16_tflops_sustained of {pk['src']} peaks (dense INT8/FP8 rate); "
                                   f"the kernel's PV half runs at the fp16 rate, so its own ceiling is 4/3 x bf16",
-                     # DRAM bytes of one attention launch: ncu measured 593.9 MB on the 1.3B-480p shape
+                     # DRAM bytes of one attention launch: ncu measured 589.1 MB on the 1.3B-480p shape
                      # (profiles/sparse_attn_kernel_wan1p3b_480p.md), equal to the compulsory operand/output bytes;
                      # scaled here by B*H*N, to which those bytes are proportional
-                     "traffic": 593.9e6 * (B * Hl * N) / (2 * 12 * 32760) if D == 128 else None},
+                     "traffic": 589.1e6 * (B * Hl * N) / (2 * 12 * 32760) if D == 128 else None},
         "e2e": e2e,
     }
     if not args.no_cpu and world == 1:
