@@ -38,6 +38,7 @@ enum {
 enum { PARO_F16 = 0, PARO_BF16 = 1 };
 enum { PARO_ROPE_NONE = 0, PARO_ROPE_REAL_F32 = 1, PARO_ROPE_COMPLEX_F64 = 2 };
 enum { PARO_NORM_NONE = 0, PARO_NORM_LAYER_HEAD = 1, PARO_NORM_RMS_ALL = 2 };
+enum { PARO_ATTN_FAST = 0, PARO_ATTN_EXACT = 1 };
 
 int paro_version(void);
 const char* paro_last_error(void);
@@ -109,7 +110,7 @@ int paro_quant_int8(const void* x, int dtype, int B, int H, int N, int D,
 
 /* Per-channel FP8-e4m3 of V written token-contiguous: v8 [B,H,D,ceil64(N)] zero padded,
  * v_scale [B,H,D] = amax/scale_max, vm [B,H,D] (mean, when smooth != 0).  v16 (nullable)
- * receives the same e4m3 values widened to fp16, the operand format of paro_sparse_attn.
+ * receives the same e4m3 values widened (exactly) to bf16, the operand format of paro_sparse_attn.
  * Replaces per_channel_fp8 (quant.py:224-293 -> fused.cu:262-427); the 16-token shuffle of
  * fused.cu:287-291 is an mma.sync artefact and is not applied. */
 int paro_quant_v_fp8(const void* v, int dtype, int B, int H, int N, int D,
@@ -202,15 +203,25 @@ int paro_plan_schedule(const int32_t* pair_ptr, const int32_t* pair_ent, int sli
  * (csrc/qattn/attn_cuda_sm80.h:19-30, qk_int_sv_f16_cuda_sm80.cu:905-1080) followed by
  * permute_attn_out (cogvideox.py:64-110).
  *   q8,k8: contiguous int8 [B,H,N,D]; q_scale [B,H,ceil(N/64)*(64/q_group)], k_scale
- *   [B,H,ceil(N/64)]; v16: fp16 [B,H,D,ceil64(N)] (e4m3 values), v_scale/vm [B,H,D] (vm may
+ *   [B,H,ceil(N/64)]; v16: bf16 [B,H,D,ceil64(N)] (e4m3 values), v_scale/vm [B,H,D] (vm may
  *   be NULL); pair_ptr from paro_plan_count, sched/sched_cnt from paro_plan_schedule (the walk
- *   order per pair of q-blocks), plan_slices = H (shared by the batch) or B*H;
+ *   order per pair of q-blocks; paro_plan_validate checks lists that were not built here),
+ *   plan_slices = H (shared by the batch) or B*H;
  *   inv_idx (nullable): table of paro_build_perm_index -- output row n_text+j of head h is
  *   stored at token n_text+inv_idx[h][j]; out: [B,H,N,D] through element strides; lse
  *   (nullable) fp32 [B,H,N] in output token order, natural log; status: int32[4] device
  *   words, zero before the first call; a non-zero word 0 makes later launches return at once.
- * S = (q8.k8^T) * q_scale * k_scale * sm_scale * log2(e); P = 2^(S - rowmax) over kept
- * blocks and columns < N; O = (P.v16) / sum(P) * v_scale + vm. */
+ * S = (q8.k8^T) * q_scale * k_scale * sm_scale * log2(e); P = 2^(S - m) over kept blocks and
+ * columns < N, rounded to bf16; O = (P.v16) / sum(P) * v_scale + vm with fp32 accumulation.
+ * mode PARO_ATTN_EXACT: m is the running row maximum (online softmax, one launch).
+ * mode PARO_ATTN_FAST (what the Python layer uses): m is fixed per row from its first kept
+ * block, which lets every step run independently of the one before; two launches: the fast
+ * walk, then the exact walk over the work items the fast one gave back because a row's
+ * scores rose more than 2^120 above its first block (usually none).  It needs the work
+ * space `redo` of paro_sparse_attn_redo_bytes(B,H,N) bytes (device memory, contents
+ * irrelevant on entry; afterwards word 0 holds the number of work items given back);
+ * calls that share a work space must be on one stream. */
+size_t paro_sparse_attn_redo_bytes(int B, int H, int N);
 int paro_sparse_attn(const int8_t* q8, const int8_t* k8, const uint16_t* v16,
                      const float* q_scale, int q_group, const float* k_scale,
                      const float* v_scale, const float* vm,
@@ -219,7 +230,8 @@ int paro_sparse_attn(const int8_t* q8, const int8_t* k8, const uint16_t* v16,
                      const int32_t* inv_idx, int n_text,
                      void* out, int out_dtype,
                      int64_t out_stride_b, int64_t out_stride_h, int64_t out_stride_n,
-                     float* lse, int B, int H, int N, int D, float sm_scale,
+                     float* lse, int B, int H, int N, int D, float sm_scale, int mode,
+                     int32_t* redo, size_t redo_bytes,
                      int32_t* status, paro_stream_t stream);
 
 /* Synchronises `stream`, copies the 4 status words to host_out (host pointer, may be NULL)

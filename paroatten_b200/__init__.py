@@ -1,6 +1,6 @@
 """paroatten_b200: PAROAttention's reordered, quantized, block-sparse attention path for
 NVIDIA B200 (sm_100a), behind the reference's `paroattention` Python names."""
-from .core import (check_status, paro_attention, paroattn, paroattn_qk_int8_pv_fp16_cuda,
+from .core import (check_status, last_redo_count, paro_attention, paroattn, paroattn_qk_int8_pv_fp16_cuda,
                    sparse_attn_quantized)
 from .host import HostPipelinedAttention, pinned_like
 from .plan import CompactPlan, PermutePlan, PlanStore, SparsePlan, compact_plan, perm_index
@@ -10,7 +10,7 @@ from .quant import (channel_mean, per_block_int8, per_channel_fp8, per_warp_int8
 from .rope import QKNorm, RopeTables, rope_permutation, rope_permute, rope_tables
 
 __all__ = [
-    "paroattn", "paroattn_qk_int8_pv_fp16_cuda", "paro_attention", "sparse_attn_quantized", "check_status",
+    "paroattn", "paroattn_qk_int8_pv_fp16_cuda", "paro_attention", "sparse_attn_quantized", "check_status", "last_redo_count",
     "PARO_CogVideoXAttnProcessor2_0", "PARO_WanAttnProcessor2_0", "TimestepCallback",
     "per_block_int8", "per_warp_int8", "sub_mean", "per_channel_fp8", "channel_mean", "prep_qk_int8", "prep_v_fp8",
     "rope_permutation", "rope_permute", "rope_tables", "RopeTables", "QKNorm",

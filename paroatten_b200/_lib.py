@@ -14,7 +14,7 @@ import threading
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_PATH = os.path.join(HERE, "libparo_b200.so")
-SOURCES = ("common.cu", "perm_plan.cu", "rope_permute.cu", "quant.cu", "sparse_attn.cu")
+SOURCES = ("common.cu", "perm_plan.cu", "rope_permute.cu", "quant.cu", "sparse_attn.cu", "sparse_attn_fast.cu")
 NVCC_FLAGS = ("-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
               "-Xcompiler", "-fPIC", "-shared")
 
@@ -22,6 +22,7 @@ PARO_OK, PARO_EINVAL, PARO_ESHAPE, PARO_EALIGN, PARO_ETIMEOUT, PARO_ECUDA, PARO_
 F16, BF16 = 0, 1
 ROPE_NONE, ROPE_REAL_F32, ROPE_COMPLEX_F64 = 0, 1, 2
 NORM_NONE, NORM_LAYER_HEAD, NORM_RMS_ALL = 0, 1, 2
+ATTN_FAST, ATTN_EXACT = 0, 1
 
 _lock = threading.Lock()
 _lib = None
@@ -104,8 +105,9 @@ SIGNATURES = {
     "paro_plan_count": (_i32, [_vp, _i32, _i32, _i32, _vp, _vp, _vp]),
     "paro_plan_fill": (_i32, [_vp, _i32, _i32, _i32, _vp, _vp, _i64, _vp, _vp, _i64, _vp]),
     "paro_plan_schedule": (_i32, [_vp, _vp, _i32, _i32, _i32, _vp, _vp, _vp]),
+    "paro_sparse_attn_redo_bytes": (_sz, [_i32, _i32, _i32]),
     "paro_sparse_attn": (_i32, [_vp, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _vp, _i32, _vp, _i32,
-                                _i64, _i64, _i64, _vp, _i32, _i32, _i32, _i32, _f32, _vp, _vp]),
+                                _i64, _i64, _i64, _vp, _i32, _i32, _i32, _i32, _f32, _i32, _vp, _sz, _vp, _vp]),
     "paro_status_poll": (_i32, [_vp, _vp, _vp]),
 }
 

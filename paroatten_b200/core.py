@@ -13,6 +13,7 @@ from .quant import (_hnd, _quant_int8, channel_mean, per_channel_fp8, per_warp_i
 from .rope import RopeTables, rope_permute
 
 _status = {}
+_redo = {}       # (device index, stream handle) -> work space of the fast walk
 _timing_sink = None  # optional list receiving (start, end) CUDA events around each attention launch
 
 
@@ -30,6 +31,27 @@ def _status_words(device: torch.device) -> torch.Tensor:
     return _status[key]
 
 
+def _redo_space(device: torch.device, B: int, H: int, N: int) -> torch.Tensor:
+    """Work space of the attention call's fast walk (the list of work items it hands to the exact
+    walk), one per device and stream: calls on different streams must not share it."""
+    need = (_lib.lib().paro_sparse_attn_redo_bytes(B, H, N) + 3) // 4
+    key = (device.index if device.index is not None else torch.cuda.current_device(), _lib.stream_ptr())
+    buf = _redo.get(key)
+    if buf is None or buf.numel() < need:
+        buf = torch.zeros(need, dtype=torch.int32, device=device)
+        _redo[key] = buf
+    return buf
+
+
+def last_redo_count(device=None) -> int:
+    """How many work items (pairs of q-blocks) of the latest attention call on the current stream the
+    fast walk handed to the exact walk (synchronises)."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    key = (device.index if device.index is not None else torch.cuda.current_device(), _lib.stream_ptr())
+    buf = _redo.get(key)
+    return 0 if buf is None else int(buf[0].item())
+
+
 def check_status(device=None) -> None:
     """Synchronises the current stream and raises if an attention launch on `device` gave up a
     bounded wait (the launch's output is then invalid)."""
@@ -42,28 +64,45 @@ def check_status(device=None) -> None:
         _lib.check(rc)
 
 
-def sparse_attn_quantized(q_int8, q_scale, k_int8, k_scale, v_f16, v_scale, vm, plan: CompactPlan, sm_scale: float,
+def sparse_attn_quantized(q_int8, q_scale, k_int8, k_scale, v16, v_scale, vm, plan: CompactPlan, sm_scale: float,
                           out_dtype=torch.bfloat16, q_group: int = 32, inv_index: Optional[torch.Tensor] = None,
                           n_text: int = 0, return_lse: bool = False, out: Optional[torch.Tensor] = None,
-                          out_layout: str = "HND"):
+                          out_layout: str = "HND", mode: str = "fast"):
     """The attention kernel on already quantised operands (HND, contiguous).
     q_int8/k_int8 int8 [B,H,N,D]; q_scale [B,H,nb*(64/q_group)]; k_scale [B,H,nb];
-    v_f16 fp16 [B,H,D,ceil64(N)] holding e4m3 values; v_scale / vm fp32 [B,H,D] (vm may be None).
+    v16 bf16 [B,H,D,ceil64(N)] holding e4m3 values; v_scale / vm fp32 [B,H,D] (vm may be None).
+    mode: "fast" (fixed reference exponent per row, exact walk only for the work items that need
+    it) or "exact" (running row maximum everywhere).
     inv_index: int32 [H, N-n_text] table from plan.perm_index -- when given, the inverse token
     permutation is applied as rows are stored.  Returns O [B,H,N,D] (or [B,N,H,D] when
     out_layout="NHD") and, if asked, LSE [B,H,N] (natural log, in output token order)."""
-    _lib.require_cuda(q_int8, k_int8, v_f16, q_scale, k_scale, v_scale, vm, inv_index)
+    _lib.require_cuda(q_int8, k_int8, v16, q_scale, k_scale, v_scale, vm, inv_index)
+    if mode not in ("fast", "exact", "fastT"):
+        raise ValueError(f"unknown mode {mode!r}")
     B, H, N, D = q_int8.shape
     nb = (N + 63) // 64
     if plan.nbq != nb or plan.nbk != nb:
         raise ValueError(f"sparse plan is {plan.nbq}x{plan.nbk} blocks but the sequence has {nb}")
     if plan.slices not in (H, B * H):
         raise ValueError(f"sparse plan has {plan.slices} slices; expected H={H} or B*H={B * H}")
-    for t, name in ((q_int8, "q_int8"), (k_int8, "k_int8"), (v_f16, "v_f16")):
+    for t, name in ((q_int8, "q_int8"), (k_int8, "k_int8"), (v16, "v16")):
         if not t.is_contiguous():
             raise ValueError(f"{name} must be contiguous")
-    if tuple(v_f16.shape) != (B, H, D, nb * 64) or v_f16.dtype != torch.float16:
-        raise ValueError("v_f16 must be fp16 [B,H,D,ceil64(N)]")
+    if q_int8.dtype != torch.int8 or k_int8.dtype != torch.int8 or tuple(k_int8.shape) != (B, H, N, D):
+        raise ValueError("q_int8 and k_int8 must be int8 [B,H,N,D]")
+    if tuple(v16.shape) != (B, H, D, nb * 64) or v16.dtype != torch.bfloat16:
+        raise ValueError("v16 must be bf16 [B,H,D,ceil64(N)]")
+    if q_group not in (32, 64):
+        raise ValueError("q_group must be 32 or 64")
+    for t, name, shape in ((q_scale, "q_scale", (B, H, nb * (64 // q_group))), (k_scale, "k_scale", (B, H, nb)),
+                           (v_scale, "v_scale", (B, H, D)), (vm, "vm", (B, H, D))):
+        if t is None and name == "vm":
+            continue
+        if t.dtype != torch.float32 or tuple(t.shape) != shape or not t.is_contiguous():
+            raise ValueError(f"{name} must be contiguous fp32 {list(shape)}")
+    if inv_index is not None and (inv_index.dtype != torch.int32 or tuple(inv_index.shape) != (H, N - n_text)
+                                  or not inv_index.is_contiguous()):
+        raise ValueError(f"inv_index must be contiguous int32 [H, N - n_text] = [{H}, {N - n_text}]")
     dev = q_int8.device
     with torch.cuda.device(dev):
         if out is None:
@@ -77,13 +116,15 @@ def sparse_attn_quantized(q_int8, q_scale, k_int8, k_scale, v_f16, v_scale, vm, 
         if sink is not None:
             ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
             ev[0].record()
+        redo = _redo_space(dev, B, H, N) if mode != "exact" else None
         _lib.check(_lib.lib().paro_sparse_attn(
-            q_int8.data_ptr(), k_int8.data_ptr(), v_f16.data_ptr(), q_scale.data_ptr(), int(q_group),
+            q_int8.data_ptr(), k_int8.data_ptr(), v16.data_ptr(), q_scale.data_ptr(), int(q_group),
             k_scale.data_ptr(), v_scale.data_ptr(), _lib.ptr(vm), plan.pair_ptr.data_ptr(), plan.sched.data_ptr(),
             plan.sched_cnt.data_ptr(),
             plan.slices, _lib.ptr(inv_index), int(n_text), out.data_ptr(), _lib.dtype_code(out.dtype),
             ov.stride(0), ov.stride(1), ov.stride(2), _lib.ptr(lse), B, H, N, D, float(sm_scale),
-            _status_words(dev).data_ptr(), _lib.stream_ptr()))
+            {"fast": _lib.ATTN_FAST, "exact": _lib.ATTN_EXACT, "fastT": 2}[mode], _lib.ptr(redo),
+            redo.numel() * 4 if redo is not None else 0, _status_words(dev).data_ptr(), _lib.stream_ptr()))
         if sink is not None:
             ev[1].record()
             sink.append(ev)
@@ -110,12 +151,13 @@ def paroattn_qk_int8_pv_fp16_cuda(q: torch.Tensor, k: torch.Tensor, v: torch.Ten
                                   sparse: Union[torch.Tensor, CompactPlan], tensor_layout: str = "HND",
                                   is_causal: bool = False, qk_quant_gran: str = "per_warp",
                                   sm_scale: Optional[float] = None, return_lse: bool = False,
-                                  smooth_k: bool = False, smooth_v: bool = True, **kwargs: Any):
+                                  smooth_k: bool = False, smooth_v: bool = True, attn_mode: str = "fast",
+                                  **kwargs: Any):
     """Same call as the reference operator (core.py:88-216): q, k, v are ALREADY in the
     reordered token order, `sparse` is the boolean block mask `[B,H,nb,nb]` (or `[H,nb,nb]`,
     shared by the batch; or an already compacted plan).  INT8 Q.K^T, fp16 P.V with fp32
     accumulation.  Unlike the reference, V is first quantised per channel to FP8-e4m3 values
-    (carried as fp16), as the fake-quant emulation this library is checked against does.
+    (carried as bf16), as the fake-quant emulation this library is checked against does.
     smooth_k defaults to False as in the reference processors (cogvideox.py:186 passes no km).
     `is_causal` is not supported (the video models never use it).  The returned LSE is that of
     the scores the kernel saw (shifted by q.mean(k) per row when smooth_k is on)."""
@@ -143,11 +185,11 @@ def paroattn_qk_int8_pv_fp16_cuda(q: torch.Tensor, k: torch.Tensor, v: torch.Ten
             # folded into Q (core.py:204-205, quant.py:91-96)
             q8, qs, k8, ks = per_block_int8(q, k, km, BLKQ=64, BLKK=64, sm_scale=sm_scale, tensor_layout=tensor_layout)
             group, scale = 64, 1.0 / 1.44269504
-        _, vs, vm, v16 = per_channel_fp8(v, tensor_layout, smooth_v=smooth_v, return_f16=True)
+        _, vs, vm, v16 = per_channel_fp8(v, tensor_layout, smooth_v=smooth_v, return_16=True)
         if tensor_layout == "NHD":
             q8, k8 = q8.transpose(1, 2), k8.transpose(1, 2)  # back to the HND buffers
         res = sparse_attn_quantized(q8, qs, k8, ks, v16, vs, vm, _as_plan(sparse), scale, out_dtype=dtype,
-                                    q_group=group, return_lse=return_lse, out_layout=tensor_layout)
+                                    q_group=group, return_lse=return_lse, out_layout=tensor_layout, mode=attn_mode)
     o, lse = res if return_lse else (res, None)
     o = o[..., :head_dim_og]
     return (o, lse) if return_lse else o
@@ -170,7 +212,7 @@ def paro_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, permute_pl
                    i_block: int = 0, i_timestep: int = 0, grid_fhw: Tuple[int, int, int], n_text: int = 0,
                    rope: Optional[RopeTables] = None, tensor_layout: str = "HND", sm_scale: Optional[float] = None,
                    smooth_k: bool = True, smooth_v: bool = True, return_lse: bool = False,
-                   q_norm=None, k_norm=None):
+                   q_norm=None, k_norm=None, attn_mode: str = "fast"):
     """The whole path of one self-attention layer, as the reference processors compose it
     (cogvideox.py:161-227): q, k, v in NATURAL token order ->
     [q_norm / k_norm (rope.QKNorm): the processors' norm_q / norm_k, applied to every token as it is read]
@@ -219,7 +261,8 @@ def paro_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, permute_pl
                                      norm=k_norm)
         v16, vs, vm, _ = prep_v_fp8(v, orders, grid, n_text, smooth_v=smooth_v, tensor_layout=tensor_layout)
         res = sparse_attn_quantized(q8, qs, k8, ks, v16, vs, vm, plan, sm_scale, out_dtype=q.dtype, q_group=32,
-                                    inv_index=index, n_text=n_text, return_lse=return_lse, out_layout=tensor_layout)
+                                    inv_index=index, n_text=n_text, return_lse=return_lse, out_layout=tensor_layout,
+                                    mode=attn_mode)
     o, lse = res if return_lse else (res, None)
     o = o[..., :head_dim_og]
     return (o, lse) if return_lse else o

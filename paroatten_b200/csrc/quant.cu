@@ -283,7 +283,7 @@ template <typename T, int D, int GM>
 __global__ void __launch_bounds__(256)
 quant_v_fp8_kernel(const T* __restrict__ v, int H, int N, int npad, int64_t sb, int64_t sh, int64_t sn,
                    const float* __restrict__ inv_tab, const float* __restrict__ mean_tab,
-                   uint8_t* __restrict__ v8, __half* __restrict__ v16, const Gather gather) {
+                   uint8_t* __restrict__ v8, __nv_bfloat16* __restrict__ v16, const Gather gather) {
   constexpr int TPR = D / 8;
   constexpr int ROWS = 256 / TPR;
   constexpr int LD = D + 8;                 // padded row, keeps 16-byte alignment
@@ -321,8 +321,10 @@ quant_v_fp8_kernel(const T* __restrict__ v, int H, int N, int npad, int64_t sb, 
     }
     const __nv_fp8x2_storage_t p = __nv_cvt_float2_to_fp8x2(make_float2(y[0], y[1]), __NV_SATFINITE, __NV_E4M3);
     if ((i & 3) == 0) w8[i / 4] = (uint32_t)p; else w8[i / 4] |= (uint32_t)p << 16;
+    // e4m3 -> fp16 -> bf16: both steps exact (3 mantissa bits, exponents inside either range)
     const __half2_raw h2 = __nv_cvt_fp8x2_to_halfraw2(p, __NV_E4M3);
-    w16[i / 2] = (uint32_t)h2.x | ((uint32_t)h2.y << 16);
+    const __nv_bfloat162 b2 = __floats2bfloat162_rn(__half2float(__half(__half_raw{h2.x})), __half2float(__half(__half_raw{h2.y})));
+    w16[i / 2] = *reinterpret_cast<const uint32_t*>(&b2);
   }
   const size_t o = ((size_t)bh * D + d) * npad + t0 + run * RUN;
 #pragma unroll
@@ -460,10 +462,10 @@ int run_v_fp8(const void* v, int B, int H, int N, int D, int64_t sb, int64_t sh,
     constexpr int GM = decltype(gm)::value == GM_PLAIN ? GM_PLAIN : GM_REORDER;
     if (D == 128)
       quant_v_fp8_kernel<T, 128, GM><<<grid, 256, 0, s>>>((const T*)v, H, N, npad, sb, sh, sn, inv_tab, mean_tab, v8,
-                                                          (__half*)v16, g);
+                                                          (__nv_bfloat16*)v16, g);
     else
       quant_v_fp8_kernel<T, 64, GM><<<grid, 256, 0, s>>>((const T*)v, H, N, npad, sb, sh, sn, inv_tab, mean_tab, v8,
-                                                         (__half*)v16, g);
+                                                         (__nv_bfloat16*)v16, g);
   });
   return check_launch("quant_v_fp8", 3);
 }

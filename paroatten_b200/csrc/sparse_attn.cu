@@ -1,4 +1,8 @@
-// Block-sparse attention over kept 64x64 blocks for sm_100a.
+// Block-sparse attention over kept 64x64 blocks for sm_100a: the walk with an EXACT running row
+// maximum (online softmax with rescaling).  paro_sparse_attn first runs the fast walk of
+// sparse_attn_fast.cu on every work item; this kernel then computes the few work items that walk gave
+// back (rows whose scores span more than its exponent range), read from the redo list, and it is the
+// reference point the fast walk is tested against.
 //
 // Work item (one CTA): a PAIR of adjacent 64-row q-blocks of one (batch, head), i.e. a 128-row
 // tile -- the native tcgen05.mma M.  The pair walks a schedule built with the plan: first the
@@ -14,14 +18,14 @@
 //               scores) of its steps, so two consecutive steps of a half are in flight at once.
 //               Online softmax in fp32 (base 2, lazy rescaling): the running row maximum passes
 //               from step to step through shared memory, each thread keeps its own share of the
-//               row sum.  P is written to TMEM as fp16; the epilogue stores O/l * v_scale + vm at
+//               row sum.  P is written to TMEM as bf16; the epilogue stores O/l * v_scale + vm at
 //               the row's un-permuted position.  These warps take the registers the others give up.
 //   warp 8      TMA producer for the K ring (int8 tiles, freed when their Q.K^T is done)
-//   warp 9      TMA producer for the V^T ring (fp16 tiles, freed when their P.V is done)
+//   warp 9      TMA producer for the V^T ring (bf16 tiles, freed when their P.V is done)
 //   warp 10     owns TMEM; one lane issues S = Q.K^T (kind::i8, A = Q from TMEM, int32 accumulators)
 //   warp 11     one lane issues O += P.V (kind::f16, A = P from TMEM, fp32 accumulators in TMEM)
 //
-// TMEM (256 columns per CTA): S [0,64) int32 scores, P [64,96) fp16 probabilities, Q [96,128) the
+// TMEM (256 columns per CTA): S [0,64) int32 scores, P [64,96) bf16 probabilities, Q [96,128) the
 // int8 query tile (A operand of Q.K^T read from TMEM, so it is not re-read from shared memory for
 // every k-block), O [128,128+D) fp32.  The softmax threads release S as soon as they hold the scores
 // in registers, so Q.K^T of step i+1 overlaps the exponentials of step i (and the other warp set
@@ -29,119 +33,30 @@
 // softmax of step i+1; two CTAs share an SM so that one CTA's softmax overlaps the other's MMAs.
 // Every wait is bounded: on expiry the CTA records a code in the status words, raises a shared
 // abort flag and unwinds (TMEM freed).
-#include <cuda_bf16.h>
-#include <cuda_fp16.h>
-
 #include <mutex>
 
-#include "common.cuh"
-#include "umma.cuh"
+#include "attn_common.cuh"
 
 namespace paro {
 
 using namespace umma;
 
-constexpr int ATT_THREADS = 384;
-constexpr int ATT_SOFTMAX_THREADS = 256;
-constexpr int TMEM_COLS = 256;
-constexpr long long WAIT_LIMIT = 400000000; // SM cycles (~0.2 s) before a wait gives up
-constexpr float SCORE_BIAS = 12582912.0f;   // 1.5 * 2^23, bit pattern 0x4B400000
-constexpr float RESCALE_TAU = 8.0f;         // rescale O only when the row max grows by > 2^8
+constexpr float RESCALE_TAU = 8.0f;            // exact walk: rescale O only when the row max grows by > 2^8
+constexpr float REF_OFFSET = 20.f;             // fixed reference: the first block's maximum maps to P = 2^-20
+constexpr float ROWSUM_LIMIT = 1.2676506e30f;  // 2^100: a step's row sum beyond it gives the pair back
 
 template <int D> struct AttnCfg {
   // Ring depths.  TMEM allows two CTAs per SM; the loads run far ahead of their use at any depth from 2
   // to 6 (same time within noise), so the rings are kept short and the shared memory left over is
   // requested back as L1 (carve-out attribute at launch) for the schedule entries and k-block scales.
-#ifndef PARO_ATT_KST128
-#define PARO_ATT_KST128 3
-#define PARO_ATT_VST128 3
-#endif
-  static constexpr int K_STAGES = (D == 128) ? PARO_ATT_KST128 : 6;
-  static constexpr int V_STAGES = (D == 128) ? PARO_ATT_VST128 : 5;
+  static constexpr int K_STAGES = (D == 128) ? 3 : 6;
+  static constexpr int V_STAGES = (D == 128) ? 3 : 5;
   static constexpr int K_BYTES = 64 * D;
-  static constexpr int V_BYTES = D * 128;   // D rows of 64 fp16
+  static constexpr int V_BYTES = D * 128;   // D rows of 64 bf16
   static constexpr int TILE_BYTES = K_STAGES * K_BYTES + V_STAGES * V_BYTES;
   static constexpr int AUX_BYTES = 4096;    // barriers, TMEM pointer, abort flag, v_scale, vm, row exchange
   static constexpr int SMEM_BYTES = TILE_BYTES + AUX_BYTES + 1024 /* alignment slack */;
 };
-
-struct AttnParams {
-  const int8_t* q8;
-  const float* q_scale;
-  const float* k_scale;
-  const float* v_scale;
-  const float* vm;
-  const int32_t* pair_ptr;
-  const uint32_t* sched;
-  const int32_t* sched_cnt;
-  const int32_t* inv_idx;
-  void* out;
-  float* lse;
-  int32_t* status;
-  int64_t osb, osh, osn;
-  int plan_slices, q_group, n_text;
-  int B, H, N, npairs, nb;
-  float scale_log2;  // sm_scale * log2(e)
-};
-
-__device__ __forceinline__ float ex2_approx(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-
-// Packed pairs of fp32 (sm_100a has 2-wide fp32 FMA / ADD).
-__device__ __forceinline__ uint64_t pack2(float a, float b) {
-  uint64_t r;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
-  return r;
-}
-__device__ __forceinline__ void unpack2(uint64_t r, float& a, float& b) {
-  asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(r));
-}
-__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
-  uint64_t r;
-  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
-  return r;
-}
-__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
-  uint64_t r;
-  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-  return r;
-}
-__device__ __forceinline__ float max3(float a, float b, float c) {
-  float r;
-  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
-  return r;
-}
-// Global load that stays where it is written (the compiler may not sink it towards its use).
-__device__ __forceinline__ uint32_t ld_pinned_u32(const uint32_t* ptr) {
-  uint32_t v;
-  asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(v) : "l"(ptr));
-  return v;
-}
-__device__ __forceinline__ void named_barrier(int id, int threads) {
-  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
-}
-
-__device__ __forceinline__ void report_timeout(const AttnParams& p, volatile int* abort_flag, int where, int iter) {
-  if (atomicCAS(p.status, 0, PARO_ETIMEOUT) == 0) {
-    p.status[1] = where;
-    p.status[2] = (int)blockIdx.x;
-    p.status[3] = iter;
-  }
-  *abort_flag = 1;
-}
-
-// Hand-off of a value between two warps through shared memory (release/acquire at CTA scope).
-__device__ __forceinline__ int ld_acquire_shared(const volatile int* ptr) {
-  int v;
-  asm volatile("ld.acquire.cta.shared.b32 %0, [%1];" : "=r"(v) : "r"(smem_u32(const_cast<const int*>(ptr))) : "memory");
-  return v;
-}
-__device__ __forceinline__ void st_release_shared(volatile int* ptr, int v) {
-  asm volatile("st.release.cta.shared.b32 [%0], %1;" ::"r"(smem_u32(const_cast<int*>(ptr))), "r"(v) : "memory");
-}
 
 #define ATT_WAIT(bar, parity, where, iter)                                   \
   if (!mbar_wait_bounded((bar), (parity), abort_flag, WAIT_LIMIT)) {         \
@@ -149,13 +64,21 @@ __device__ __forceinline__ void st_release_shared(volatile int* ptr, int v) {
     break;                                                                   \
   }
 
-template <int D, typename OutT>
+// FIXED = false: exact running row maximum (online softmax, lazy rescaling of O).
+// FIXED = true:  the row's reference exponent is fixed when its FIRST kept block has been seen (that
+//   block's maximum + REF_OFFSET) and P = 2^(s - m_ref) is kept in bf16 (8 exponent bits) and summed in
+//   fp32, so scores up to 2^100 above the first block are representable and nothing is ever rescaled:
+//   no per-step maximum, no maximum handed between the warp sets, no accumulator read-modify-write.
+//   A step whose row sum leaves that range (or is not finite) makes the CTA give its work item back
+//   through the redo list instead of storing it; the exact walk then computes that pair.
+template <int D, typename OutT, bool FIXED>
 __global__ void __launch_bounds__(ATT_THREADS, 2)
 sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
-                   const AttnParams p) {
+                         const AttnParams p) {
   using Cfg = AttnCfg<D>;
   constexpr int KST = Cfg::K_STAGES, VST = Cfg::V_STAGES;
-  if (*reinterpret_cast<volatile int32_t*>(p.status) != 0) return;  // an earlier CTA failed: drain quickly
+  // second launch of a call: only the work items the fast walk gave back
+  if (p.from_list && (int)blockIdx.x >= *reinterpret_cast<volatile int32_t*>(p.redo)) return;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -173,18 +96,27 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
   uint64_t* bar_sfree = bar_sready + 4;                 // [2][2]  ... copied to registers
   uint64_t* bar_pready = bar_sfree + 4;                 // [2][2]  P of (half, step parity) written
   uint64_t* bar_pvdone = bar_pready + 4;                // [2][2]  P.V of (half, step parity) finished
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_pvdone + 4);
+  uint64_t* bar_drain = bar_pvdone + 4;                 // [2]     issuers' MMAs retired (abort path only)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_drain + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  volatile int* s_mstep = abort_flag + 1;                  // [4]  steps whose row maxima are published, per quadrant
+  volatile int* s_drain = abort_flag + 1;                  // 1: an earlier launch or CTA failed, leave at once
+  volatile int* s_redo = s_drain + 1;                      // 1: a row sum left the fixed-reference range
+  volatile int* s_mstep = s_redo + 1;                      // [4]  steps whose row maxima are published, per quadrant
   float* s_vscale = reinterpret_cast<float*>(aux + 512);   // [D]
   float* s_vm = s_vscale + D;                              // [D]
   volatile float* s_mrow = reinterpret_cast<volatile float*>(aux + 1536);   // [128] running row maximum
   float* s_xl = reinterpret_cast<float*>(aux + 2048);                       // [2][128] row-sum exchange
   static_assert(512 + 2 * D * 4 <= 1536 && 2048 + 2 * 128 * 4 <= Cfg::AUX_BYTES, "aux area too small");
-  static_assert((17 + 2 * KST + 2 * VST) * 8 + 8 + 20 <= 512, "barrier area too small");
+  static_assert((19 + 2 * KST + 2 * VST) * 8 + 8 + 28 <= 512, "barrier area too small");
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int bh = blockIdx.x / p.npairs, pair = blockIdx.x % p.npairs;
+  // one thread decides for the whole CTA whether an earlier failure makes this launch drain (every
+  // thread reading the word for itself could split the CTA around the collective operations below)
+  if (threadIdx.x == 0) *s_drain = *reinterpret_cast<volatile int32_t*>(p.status) != 0;
+  __syncthreads();
+  if (*s_drain) return;
+  const int item = p.from_list ? p.redo[REDO_HEADER + blockIdx.x] : (int)blockIdx.x;
+  const int bh = item / p.npairs, pair = item % p.npairs;
   const int slice = bh % p.plan_slices;
   // The pair's schedule: entry i = kbA | kbB << 16 (0xFFFF: no tile for that half in step i).  First
   // the k-blocks both halves keep (kbA == kbB: one K/V tile, one full-height MMA group), then the
@@ -223,7 +155,10 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
       mbar_init(bar_pvdone + i, 1);
       s_mstep[i] = 0;
     }
+    mbar_init(bar_drain, 1);
+    mbar_init(bar_drain + 1, 1);
     *abort_flag = 0;
+    *s_redo = 0;
     fence_barrier_init();
   }
   if (warp == 10) {
@@ -253,16 +188,18 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
         for (int j = 0; j < 2; ++j) {
           if (!act_[j]) continue;
           const int st = t % KST, use = t / KST;
-          ++t;
           if (use > 0 && !mbar_wait_bounded(bar_kfree + st, (use - 1) & 1, abort_flag, WAIT_LIMIT)) {
             report_timeout(p, abort_flag, 1, i);
             ok = false;
             break;
           }
+          ++t;
           mbar_arrive_expect_tx(bar_kfull + st, Cfg::K_BYTES);
           tma_load_3d(sK + st * Cfg::K_BYTES, &tm_k, 0, kblk_[j] * 64, bh, bar_kfull + st);
         }
       }
+      if (*abort_flag)   // leaving early: the copies this thread started must have landed first
+        for (int u = max(0, t - KST); u < t; ++u) mbar_wait_plain_bounded(bar_kfull + u % KST, (u / KST) & 1, WAIT_LIMIT);
     } else if (warp == 9 && lane == 0) {
       // ---------------------------------------------------------------- TMA producer: V ring
       tma_prefetch_desc(&tm_v);
@@ -277,16 +214,18 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
         for (int j = 0; j < 2; ++j) {
           if (!act_[j]) continue;
           const int st = t % VST, use = t / VST;
-          ++t;
           if (use > 0 && !mbar_wait_bounded(bar_vfree + st, (use - 1) & 1, abort_flag, WAIT_LIMIT)) {
             report_timeout(p, abort_flag, 9, i);
             ok = false;
             break;
           }
+          ++t;
           mbar_arrive_expect_tx(bar_vfull + st, Cfg::V_BYTES);
           tma_load_3d(sV + st * Cfg::V_BYTES, &tm_v, kblk_[j] * 64, 0, bh, bar_vfull + st);
         }
       }
+      if (*abort_flag)
+        for (int u = max(0, t - VST); u < t; ++u) mbar_wait_plain_bounded(bar_vfull + u % VST, (u / VST) & 1, WAIT_LIMIT);
     } else if (warp == 10 && lane == 0) {
       // ---------------------------------------------------------------- MMA issuer: S = Q.K^T
       // (the two issuers are separate threads so that a P.V group waiting for room in the tensor
@@ -332,9 +271,13 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
           }
         }
       } while (false);
+      if (*abort_flag) {   // the MMAs issued so far must retire before tensor memory is freed
+        mma_commit(bar_drain);
+        mbar_wait_plain_bounded(bar_drain, 0, WAIT_LIMIT);
+      }
     } else if (warp == 11 && lane == 0) {
       // ---------------------------------------------------------------- MMA issuer: O += P.V
-      constexpr uint32_t IDESC_PV = instr_desc(1, 0, 0, 128, D);   // f32 += f16 * f16
+      constexpr uint32_t IDESC_PV = instr_desc(1, 1, 1, 128, D);   // f32 += bf16 * bf16
       bool ok = true;
       int t = 0;
       uint32_t e_cur = n_steps > 0 ? sched[0] : 0u, e_nxt = n_steps > 1 ? sched[1] : 0u;
@@ -370,6 +313,10 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
           if (w != 0) mma_commit(bar_pvdone + 2 + par);
         }
       }
+      if (*abort_flag) {
+        mma_commit(bar_drain + 1);
+        mbar_wait_plain_bounded(bar_drain + 1, 0, WAIT_LIMIT);
+      }
     }
   } else {
     // ------------------------------------------------------------------ softmax + epilogue
@@ -404,10 +351,14 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
       if (lane == 0) mbar_arrive(bar_q);
     }
     const int per_bh = p.nb * (64 / p.q_group);
-    const float rowscale = (tok < p.N ? p.q_scale[(size_t)bh * per_bh + tok / p.q_group] : 0.f) * p.scale_log2;
+    // rows past the end of the sequence: scale 0, or (fixed reference) a tiny positive one -- there the
+    // -inf of masked columns times 0 would be a NaN that reads as a row sum out of range
+    const float rowscale = tok < p.N ? p.q_scale[(size_t)bh * per_bh + tok / p.q_group] * p.scale_log2
+                                     : (FIXED ? 1e-30f : 0.f);
     // l: this thread's share of the row sum (the steps of its parity), relative to the maximum m_l
-    float m_l = -INFINITY, l = 0.f;
-    bool ok = true;
+    // (exact walk) or to the row's fixed reference exponent m_ref
+    float m_l = -INFINITY, l = 0.f, m_ref = 0.f;
+    bool ok = true, redo = false;
     auto wait_bar = [&](uint64_t* bar, int phase, int code, int i) {
       const bool good = __all_sync(0xffffffffu, mbar_wait_bounded(bar, phase & 1, abort_flag, WAIT_LIMIT));
       if (!good) report_timeout(p, abort_flag, code, i);
@@ -419,13 +370,15 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
     uint64_t* const my_pready = bar_pready + 2 * half + set;
     uint64_t* const prev_pvdone = bar_pvdone + 2 * half + (set ^ 1);   // P.V of the steps of the other parity
     const float* kscale_bh = p.k_scale + (size_t)bh * p.nb;
-    int kb_next = set < n_mine ? my_kb(set) : 0;
+    // (a k-block id beyond the sequence can only come from a malformed plan; clamped so that the scale
+    // look-up stays inside its array)
+    int kb_next = set < n_mine ? min(my_kb(set), p.nb - 1) : 0;
     float ks_next = set < n_mine ? kscale_bh[kb_next] : 0.f;
     for (int i = set; i < n_mine; i += 2) {   // the two halves only meet in the issuers' queues
       const int kb = kb_next;
       const float kscale = ks_next;
       if (i + 2 < n_mine) {   // fetched one step ahead so that the loads are off the critical path
-        kb_next = my_kb(i + 2);
+        kb_next = min(my_kb(i + 2), p.nb - 1);
         ks_next = kscale_bh[kb_next];
       }
       ok = wait_bar(my_sready, i >> 1, 6, i);
@@ -454,18 +407,46 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
         for (int j = 0; j < 64; ++j)
           if (j >= valid) f[j] = -INFINITY;
       }
-      float mx4[4] = {f[0], f[1], f[2], f[3]};   // four independent chains of 3-input max
-#pragma unroll
-      for (int j = 4; j < 64; j += 8) {
-        mx4[0] = max3(mx4[0], f[j], f[j + 1]);
-        mx4[1] = max3(mx4[1], f[j + 2], f[j + 3]);
-        if (j + 4 < 64) {
-          mx4[2] = max3(mx4[2], f[j + 4], f[j + 5]);
-          mx4[3] = max3(mx4[3], f[j + 6], f[j + 7]);
-        }
-      }
       const float sc = rowscale * kscale;
-      const float mx = (fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) - SCORE_BIAS) * sc;
+      auto row_max = [&]() {   // maximum of the step's scores, in the exponent's units
+        float mx4[4] = {f[0], f[1], f[2], f[3]};   // four independent chains of 3-input max
+#pragma unroll
+        for (int j = 4; j < 64; j += 8) {
+          mx4[0] = max3(mx4[0], f[j], f[j + 1]);
+          mx4[1] = max3(mx4[1], f[j + 2], f[j + 3]);
+          if (j + 4 < 64) {
+            mx4[2] = max3(mx4[2], f[j + 4], f[j + 5]);
+            mx4[3] = max3(mx4[3], f[j + 6], f[j + 7]);
+          }
+        }
+        return (fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) - SCORE_BIAS) * sc;
+      };
+      float m_new;
+      bool pv_consumed = (i == 0);
+      if constexpr (FIXED) {
+        if (i == 0) {
+          m_ref = row_max() + REF_OFFSET;
+          s_mrow[r] = m_ref;
+          __syncwarp();
+          if (lane == 0) st_release_shared(s_mstep + qd, 1);
+        } else if (i == 1) {   // the other warp set fixed the reference in step 0
+          bool seen = ld_acquire_shared(s_mstep + qd) != 0;
+          if (!seen) {
+            const long long t0 = clock64();
+            while (!(seen = ld_acquire_shared(s_mstep + qd) != 0)) {
+              if (*abort_flag || clock64() - t0 > WAIT_LIMIT) break;
+            }
+          }
+          if (!__all_sync(0xffffffffu, seen)) {
+            report_timeout(p, abort_flag, 10, i);
+            ok = false;
+            break;
+          }
+          m_ref = s_mrow[r];
+        }
+        m_new = m_ref;
+      } else {
+      const float mx = row_max();
       // The running maximum of the row passes between the two threads that share it through shared
       // memory: step i reads what step i-1 (the other warp set) published.
       float m_old = -INFINITY;
@@ -484,7 +465,7 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
         }
         m_old = s_mrow[r];
       }
-      float m_new = m_old;
+      m_new = m_old;
       bool resc = false;
       if (mx > m_old + RESCALE_TAU) {   // lazy: the maximum only moves when it grows by more than 2^tau
         m_new = mx;
@@ -497,7 +478,6 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
         l *= ex2_approx(m_l - m_new);     // 0 when m_l = -inf
         m_l = m_new;
       }
-      bool pv_consumed = (i == 0);
       if (__any_sync(0xffffffffu, resc)) {  // O may only be touched once this half's previous P.V has landed
         pv_consumed = true;
         ok = wait_bar(prev_pvdone, (i - 1) >> 1, 7, i);
@@ -516,6 +496,7 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
         }
         tmem_wait_st();
       }
+      }   // exact walk
       const float xoff = fmaf(-SCORE_BIAS, sc, -m_new);   // (bias + s) * sc + xoff = s * sc - m
       const uint64_t sc2 = pack2(sc, sc), negm2 = pack2(xoff, xoff);
       uint64_t sum2[2] = {0ull, 0ull};
@@ -528,17 +509,17 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
           unpack2(fma2(pack2(f[32 * c + 2 * j], f[32 * c + 2 * j + 1]), sc2, negm2), x0, x1);
           const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);   // 2^-inf = 0 for masked columns
           sum2[j & 1] = add2(sum2[j & 1], pack2(p0, p1));
-          const __half2 h2 = __floats2half2_rn(p0, p1);
-          pk[j] = *reinterpret_cast<const uint32_t*>(&h2);
+          pk[j] = pack_bf16x2(p0, p1);
         }
         // P of this half is rewritten only after the P.V that read its previous contents (the other
         // warp set's step) has finished
         if (c == 0 && !pv_consumed) ok = wait_bar(prev_pvdone, (i - 1) >> 1, 7, i);
-        tmem_st16(tP + lane_off + 16 * c, pk);   // fp16 P: two values per 32-bit column
+        tmem_st16(tP + lane_off + 16 * c, pk);   // bf16 P: two values per 32-bit column
       }
       if (!ok) break;
       float sa, sb;
       unpack2(add2(sum2[0], sum2[1]), sa, sb);
+      if constexpr (FIXED) redo = redo || !(sa + sb < ROWSUM_LIMIT);   // out of range, or NaN
       l += sa + sb;
       tmem_wait_st();
       tc_fence_before();
@@ -551,13 +532,20 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
     if (ok && n_mine > 0) ok = wait_bar(bar_pvdone + 2 * half + ((n_mine - 1) & 1), (n_mine - 1) >> 1, 8, n_mine);
     // final maximum and row sum = both threads' shares (reached by every softmax thread, also
     // after a failed wait)
+    if (FIXED && redo) *s_redo = 1;
     named_barrier(1, ATT_SOFTMAX_THREADS);
     const float m = n_mine > 0 ? s_mrow[r] : -INFINITY;
-    if (m_l != m) l *= ex2_approx(m_l - m);
+    if (!FIXED && m_l != m) l *= ex2_approx(m_l - m);
     s_xl[set * 128 + r] = l;
     named_barrier(1, ATT_SOFTMAX_THREADS);
     l += s_xl[(set ^ 1) * 128 + r];
-    if (ok) {
+    ok = ok && !*abort_flag;
+    const bool give_back = FIXED && *s_redo != 0;
+    if (ok && give_back && threadIdx.x == 0) {
+      const int slot = atomicAdd(p.redo, 1);
+      p.redo[REDO_HEADER + slot] = item;
+    }
+    if (ok && !give_back) {
       const int b = bh / p.H, h = bh % p.H;
       const bool live = tok < p.N;
       int dst = tok;
@@ -621,8 +609,7 @@ static EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// 3-D map over a tensor [d2][d1][d0] of `esize`-byte elements, box [1][box1][box0].
-static int make_map(CUtensorMap* map, CUtensorMapDataType dt, int esize, const void* base, uint64_t d0, uint64_t d1,
+int make_tensor_map(CUtensorMap* map, CUtensorMapDataType dt, int esize, const void* base, uint64_t d0, uint64_t d1,
                     uint64_t d2, uint32_t box0, uint32_t box1, CUtensorMapSwizzle swz) {
   EncodeTiledFn fn = encode_fn();
   PARO_REQUIRE(fn != nullptr, PARO_ECUDA, "cuTensorMapEncodeTiled is not available from this driver");
@@ -636,30 +623,52 @@ static int make_map(CUtensorMap* map, CUtensorMapDataType dt, int esize, const v
   return PARO_OK;
 }
 
-template <int D, typename OutT>
-static int launch_attn(const int8_t* q8, const int8_t* k8, const uint16_t* v16, const AttnParams& p, cudaStream_t s) {
+template <int D, typename OutT, bool FIXED>
+static int launch_walk(const int8_t* k8, const uint16_t* v16, const AttnParams& p, unsigned ctas, cudaStream_t s) {
   using Cfg = AttnCfg<D>;
   const uint64_t BH = (uint64_t)p.B * p.H;
   const uint64_t npad = (uint64_t)p.nb * 64;
   const CUtensorMapSwizzle swz_qk = D == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
   CUtensorMap tk, tv;
-  if (int rc = make_map(&tk, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, k8, D, p.N, BH, D, 64, swz_qk)) return rc;
-  if (int rc = make_map(&tv, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, v16, npad, D, BH, 64, D, CU_TENSOR_MAP_SWIZZLE_128B))
+  if (int rc = make_tensor_map(&tk, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, k8, D, p.N, BH, D, 64, swz_qk)) return rc;
+  if (int rc = make_tensor_map(&tv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, v16, npad, D, BH, 64, D, CU_TENSOR_MAP_SWIZZLE_128B))
     return rc;
-  auto kern = sparse_attn_kernel<D, OutT>;
+  auto kern = sparse_attn_kernel<D, OutT, FIXED>;
   PARO_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
   // shared memory for two CTAs per SM and no more: the rest of the 256 KB serves as L1
   constexpr int carveout_pct = (2 * (Cfg::SMEM_BYTES + 1024) * 100 + 228 * 1024 - 1) / (228 * 1024);
   PARO_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, carveout_pct < 100 ? carveout_pct : 100));
-  const uint64_t ctas = BH * p.npairs;
-  PARO_REQUIRE(ctas < (1ull << 31), PARO_ESHAPE, "paro_sparse_attn: too many work items");
-  kern<<<(unsigned)ctas, ATT_THREADS, Cfg::SMEM_BYTES, s>>>(tk, tv, p);
+  kern<<<ctas, ATT_THREADS, Cfg::SMEM_BYTES, s>>>(tk, tv, p);
   return check_launch("sparse_attn_kernel");
+}
+
+int launch_attn_exact(const int8_t* k8, const uint16_t* v16, const AttnParams& p, int D, int out_dtype, unsigned ctas,
+                      cudaStream_t s) {
+  if (D == 128)
+    return out_dtype == PARO_F16 ? launch_walk<128, __half, false>(k8, v16, p, ctas, s)
+                                 : launch_walk<128, __nv_bfloat16, false>(k8, v16, p, ctas, s);
+  return out_dtype == PARO_F16 ? launch_walk<64, __half, false>(k8, v16, p, ctas, s)
+                               : launch_walk<64, __nv_bfloat16, false>(k8, v16, p, ctas, s);
+}
+
+int launch_attn_fixed(const int8_t* k8, const uint16_t* v16, const AttnParams& p, int D, int out_dtype, unsigned ctas,
+                      cudaStream_t s) {
+  if (D == 128)
+    return out_dtype == PARO_F16 ? launch_walk<128, __half, true>(k8, v16, p, ctas, s)
+                                 : launch_walk<128, __nv_bfloat16, true>(k8, v16, p, ctas, s);
+  return out_dtype == PARO_F16 ? launch_walk<64, __half, true>(k8, v16, p, ctas, s)
+                               : launch_walk<64, __nv_bfloat16, true>(k8, v16, p, ctas, s);
 }
 
 }  // namespace paro
 
 using namespace paro;
+
+extern "C" size_t paro_sparse_attn_redo_bytes(int B, int H, int N) {
+  if (B <= 0 || H <= 0 || N <= 0) return 0;
+  const size_t nb = ((size_t)N + 63) / 64;
+  return sizeof(int32_t) * (REDO_HEADER + (size_t)B * H * ((nb + 1) / 2));
+}
 
 extern "C" int paro_sparse_attn(const int8_t* q8, const int8_t* k8, const uint16_t* v16,
                                 const float* q_scale, int q_group, const float* k_scale,
@@ -669,7 +678,8 @@ extern "C" int paro_sparse_attn(const int8_t* q8, const int8_t* k8, const uint16
                                 const int32_t* inv_idx, int n_text,
                                 void* out, int out_dtype,
                                 int64_t out_stride_b, int64_t out_stride_h, int64_t out_stride_n,
-                                float* lse, int B, int H, int N, int D, float sm_scale,
+                                float* lse, int B, int H, int N, int D, float sm_scale, int mode,
+                                int32_t* redo, size_t redo_bytes,
                                 int32_t* status, paro_stream_t stream) {
   PARO_REQUIRE(q8 && k8 && v16 && q_scale && k_scale && v_scale && pair_ptr && sched && sched_cnt && out && status, PARO_EINVAL,
                "paro_sparse_attn: null pointer");
@@ -685,20 +695,30 @@ extern "C" int paro_sparse_attn(const int8_t* q8, const int8_t* k8, const uint16
   PARO_REQUIRE(out_stride_b % 8 == 0 && out_stride_h % 8 == 0 && out_stride_n % 8 == 0 && out_stride_n >= D,
                PARO_EALIGN, "paro_sparse_attn: output strides must be multiples of 8 elements");
   PARO_REQUIRE(sm_scale > 0.f, PARO_EINVAL, "paro_sparse_attn: sm_scale must be positive");
+  PARO_REQUIRE(mode == PARO_ATTN_FAST || mode == PARO_ATTN_EXACT || mode == 2, PARO_EINVAL, "paro_sparse_attn: unknown mode %d", mode);
+  PARO_REQUIRE(mode == PARO_ATTN_EXACT || (redo && redo_bytes >= paro_sparse_attn_redo_bytes(B, H, N)), PARO_ECAP,
+               "paro_sparse_attn: the fast walk needs a redo work space of paro_sparse_attn_redo_bytes() bytes");
   AttnParams p;
   p.q8 = q8; p.q_scale = q_scale; p.k_scale = k_scale; p.v_scale = v_scale; p.vm = vm;
   p.pair_ptr = pair_ptr; p.sched = sched; p.sched_cnt = sched_cnt; p.inv_idx = inv_idx;
-  p.out = out; p.lse = lse; p.status = status;
+  p.out = out; p.lse = lse; p.status = status; p.redo = redo;
   p.osb = out_stride_b; p.osh = out_stride_h; p.osn = out_stride_n;
   p.plan_slices = plan_slices; p.q_group = q_group; p.n_text = n_text;
   p.B = B; p.H = H; p.N = N; p.nb = (N + 63) / 64; p.npairs = (p.nb + 1) / 2;
+  p.from_list = 0;
   p.scale_log2 = sm_scale * 1.44269504f;
   cudaStream_t s = (cudaStream_t)stream;
-  if (D == 128)
-    return out_dtype == PARO_F16 ? launch_attn<128, __half>(q8, k8, v16, p, s)
-                                 : launch_attn<128, __nv_bfloat16>(q8, k8, v16, p, s);
-  return out_dtype == PARO_F16 ? launch_attn<64, __half>(q8, k8, v16, p, s)
-                               : launch_attn<64, __nv_bfloat16>(q8, k8, v16, p, s);
+  const uint64_t ctas = (uint64_t)B * H * p.npairs;
+  PARO_REQUIRE(ctas < (1ull << 31), PARO_ESHAPE, "paro_sparse_attn: too many work items");
+  if (mode == PARO_ATTN_EXACT) return launch_attn_exact(k8, v16, p, D, out_dtype, (unsigned)ctas, s);
+  // fast walk over every work item, then the exact walk over the items it gave back (usually none:
+  // the second launch's CTAs then leave at once)
+  PARO_CUDA_OK(cudaMemsetAsync(redo, 0, sizeof(int32_t) * REDO_HEADER, s));
+  if (int rc = mode == 2 ? launch_attn_fast(k8, v16, p, D, out_dtype, (unsigned)ctas, s)
+                         : launch_attn_fixed(k8, v16, p, D, out_dtype, (unsigned)ctas, s))
+    return rc;
+  p.from_list = 1;
+  return launch_attn_exact(k8, v16, p, D, out_dtype, (unsigned)ctas, s);
 }
 
 

@@ -67,6 +67,17 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
   return true;
 }
 
+// The same without an abort flag: used by a role that is already leaving and only has to see its own
+// copies or MMAs retire before the CTA's shared and tensor memory are handed on.
+__device__ __forceinline__ bool mbar_wait_plain_bounded(uint64_t* bar, uint32_t parity, long long limit_cycles) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (!mbar_try_wait_suspend(bar, parity, 20000u)) {
+    if (clock64() - t0 > limit_cycles) return false;
+  }
+  return true;
+}
+
 // ----- TMA -----------------------------------------------------------------------------------
 __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, int c0, int c1, int c2,
                                             uint64_t* bar) {
@@ -216,6 +227,27 @@ __device__ __forceinline__ void mma_f16_ts_masked(uint32_t d_tmem, uint32_t a_tm
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %6, %7, %8}, p;\n\t}"
       ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(m0), "r"(m1), "r"(m2), "r"(m3)
+      : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem]^T, 16-bit float operands (formats in the instruction descriptor), fp32 accumulator.
+__device__ __forceinline__ void mma_f16_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                           uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// int8 operands both from shared memory, with a 128-bit mask of accumulator lanes that are NOT written.
+__device__ __forceinline__ void mma_i8_ss_masked(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                 uint32_t accumulate, uint32_t m0, uint32_t m1, uint32_t m2,
+                                                 uint32_t m3) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(m0), "r"(m1), "r"(m2), "r"(m3)
       : "memory");
 }
 // Arrives once on `bar` when every tcgen05.mma issued so far by this thread has completed.

@@ -103,18 +103,18 @@ def sub_mean(v: torch.Tensor, tensor_layout: str = "HND"):
 
 
 def per_channel_fp8(v: torch.Tensor, tensor_layout: str = "HND", scale_max: float = 448.0, smooth_v: bool = True,
-                    return_f16: bool = False):
+                    return_16: bool = False):
     """Reference signature paroattention/quant.py:224-293: V transposed to token-contiguous
     [B,H,D,ceil64(N)] float8_e4m3fn (zero padded; no 16-token shuffle), per-channel scale
-    [B,H,D] and mean [B,H,D] (None without smoothing).  return_f16=True appends the same values
-    widened to fp16, which is what the attention kernel consumes."""
+    [B,H,D] and mean [B,H,D] (None without smoothing).  return_16=True appends the same values
+    widened to bf16 (exact), which is what the attention kernel consumes."""
     _lib.require_cuda(v)
     vv = _hnd(v, tensor_layout)
     B, H, N, D = vv.shape
     npad = (N + 63) // 64 * 64
     with torch.cuda.device(v.device):
         v8 = torch.empty(B, H, D, npad, dtype=torch.float8_e4m3fn, device=v.device)
-        v16 = torch.empty(B, H, D, npad, dtype=torch.float16, device=v.device) if return_f16 else None
+        v16 = torch.empty(B, H, D, npad, dtype=torch.bfloat16, device=v.device) if return_16 else None
         scale = torch.empty(B, H, D, dtype=torch.float32, device=v.device)
         vm = torch.empty(B, H, D, dtype=torch.float32, device=v.device) if smooth_v else None
         scr = _stats_scratch(B, H, N, D, v.device)
@@ -124,7 +124,7 @@ def per_channel_fp8(v: torch.Tensor, tensor_layout: str = "HND", scale_max: floa
             scr.data_ptr(), scr.numel(), _lib.stream_ptr()))
     if tensor_layout == "NHD":
         v8 = v8.transpose(1, 2)  # [B,D,H,Npad] view, the reference's NHD output shape
-    return (v8, scale, vm, v16) if return_f16 else (v8, scale, vm)
+    return (v8, scale, vm, v16) if return_16 else (v8, scale, vm)
 
 
 def prep_qk_int8(x: torch.Tensor, order_ids: Optional[torch.Tensor], grid, n_text: int = 0, rope=None, group: int = 32,
@@ -170,8 +170,8 @@ def prep_qk_int8(x: torch.Tensor, order_ids: Optional[torch.Tensor], grid, n_tex
 def prep_v_fp8(v: torch.Tensor, order_ids: Optional[torch.Tensor], grid, n_text: int = 0, smooth_v: bool = True,
                scale_max: float = 448.0, tensor_layout: str = "HND", want_fp8: bool = False):
     """Per-head reordering + per-channel FP8 quantisation of V from the natural-order tensor.
-    Returns (v_f16 [B,H,D,ceil64(N)] holding the e4m3 values, v_scale, vm, v_fp8 or None), equal
-    bit for bit to per_channel_fp8(rope_permute(v, ...), return_f16=True)."""
+    Returns (v16: bf16 [B,H,D,ceil64(N)] holding the e4m3 values, v_scale, vm, v_fp8 or None), equal
+    bit for bit to per_channel_fp8(rope_permute(v, ...), return_16=True)."""
     _lib.require_cuda(v, order_ids)
     vv = _hnd(v, tensor_layout)
     B, H, N, D = vv.shape
@@ -180,7 +180,7 @@ def prep_v_fp8(v: torch.Tensor, order_ids: Optional[torch.Tensor], grid, n_text:
     with torch.cuda.device(v.device):
         if order_ids is not None:
             order_ids = order_ids.to(device=v.device, dtype=torch.int32).contiguous()
-        v16 = torch.empty(B, H, D, npad, dtype=torch.float16, device=v.device)
+        v16 = torch.empty(B, H, D, npad, dtype=torch.bfloat16, device=v.device)
         v8 = torch.empty(B, H, D, npad, dtype=torch.float8_e4m3fn, device=v.device) if want_fp8 else None
         scale = torch.empty(B, H, D, dtype=torch.float32, device=v.device)
         vm = torch.empty(B, H, D, dtype=torch.float32, device=v.device) if smooth_v else None

@@ -40,8 +40,10 @@ def quantised(q, k, v, orders, grid, n_text=0):
     (64, 976, 2, 0.3, torch.bfloat16),      # tail 16, odd block count (pair with a missing half)
     (128, 4160, 2, 0.2, torch.bfloat16),    # 65 blocks: long lists, ring wrap-around
 ])
-def test_kernel_on_oracle_quantised_operands(D, N, H, density, dtype):
-    """The kernel alone: operands quantised by the ORACLE, so only the attention differs."""
+@pytest.mark.parametrize("mode", ["fast", "exact"])
+def test_kernel_on_oracle_quantised_operands(D, N, H, density, dtype, mode):
+    """The kernel alone: operands quantised by the ORACLE, so only the attention differs.  Both
+    walks: the fast one (fixed reference exponent per row) and the exact one (running maximum)."""
     B = 2
     q, k, v, _ = po.make_inputs(B, H, N, D, dtype, seed=N + D)
     nb = (N + 63) // 64
@@ -49,18 +51,26 @@ def test_kernel_on_oracle_quantised_operands(D, N, H, density, dtype):
     q8, qs, k8, ks, v8, vs, vm = quantised(q, k, v, [0] * H, (1, 1, N))
     want, want_lse = po.sparse_attention(q8, qs, k8, ks, v8, vs, vm, mask, D ** -0.5, out_dtype=dtype, return_lse=True)
     plan = pb.compact_plan(mask.to(DEV))
-    got, lse = pb.sparse_attn_quantized(q8.to(DEV), qs.to(DEV), k8.to(DEV), ks.to(DEV), v8.to(torch.float16).to(DEV),
-                                        vs.to(DEV), vm.to(DEV), plan, D ** -0.5, out_dtype=dtype, return_lse=True)
+    got, lse = pb.sparse_attn_quantized(q8.to(DEV), qs.to(DEV), k8.to(DEV), ks.to(DEV), v8.to(torch.bfloat16).to(DEV),
+                                        vs.to(DEV), vm.to(DEV), plan, D ** -0.5, out_dtype=dtype, return_lse=True,
+                                        mode=mode)
     pb.check_status()
-    assert_close(got, want, f"D={D} N={N}")
+    if mode == "fast":
+        assert pb.last_redo_count() == 0      # N(0,1) data never leaves the fast walk's exponent range
+    assert_close(got, want, f"D={D} N={N} {mode}")
     assert (lse.cpu() - want_lse).abs().max().item() < 2e-3
 
 
-@pytest.mark.parametrize("D,growth", [(128, 1.0), (64, 1.0), (128, -1.0), (128, 0.25)])
-def test_row_maximum_that_keeps_growing(D, growth):
+@pytest.mark.parametrize("D,growth,mode", [(128, 1.0, "exact"), (64, 1.0, "exact"), (128, -1.0, "exact"),
+                                           (128, 0.25, "exact"), (128, 1.0, "fast"), (64, 0.25, "fast"),
+                                           (128, 6.0, "fast"), (64, 6.0, "fast"), (128, -6.0, "fast")])
+def test_row_maximum_that_keeps_growing(D, growth, mode):
     """Keys of later blocks are scaled up (or down), so that along every row's list the running
-    maximum rises by more than the lazy-rescaling threshold again and again: the accumulator is
-    rescaled by the warp set whose step saw the rise, and the other set picks the new maximum up."""
+    maximum rises by more than the lazy-rescaling threshold again and again.  Exact walk: the
+    accumulator is rescaled by the warp set whose step saw the rise, and the other set picks the new
+    maximum up.  Fast walk: moderate growth stays inside its exponent range; with growth 6 the scores
+    of late blocks lie hundreds of powers of two above a row's first block, so pairs of q-blocks are
+    handed to the exact walk (the redo count says so) and the result is still the oracle's."""
     B, H, N = 1, 2, 1024
     q, k, v, _ = po.make_inputs(B, H, N, D, torch.bfloat16, seed=77)
     nb = N // 64
@@ -72,12 +82,15 @@ def test_row_maximum_that_keeps_growing(D, growth):
     want, want_lse = po.sparse_attention(q8, qs, k8, ks, v8, vs, vm, mask, D ** -0.5, out_dtype=torch.bfloat16,
                                          return_lse=True)
     plan = pb.compact_plan(mask.to(DEV))
-    got, lse = pb.sparse_attn_quantized(q8.to(DEV), qs.to(DEV), k8.to(DEV), ks.to(DEV), v8.to(torch.float16).to(DEV),
+    got, lse = pb.sparse_attn_quantized(q8.to(DEV), qs.to(DEV), k8.to(DEV), ks.to(DEV), v8.to(torch.bfloat16).to(DEV),
                                         vs.to(DEV), vm.to(DEV), plan, D ** -0.5, out_dtype=torch.bfloat16,
-                                        return_lse=True)
+                                        return_lse=True, mode=mode)
     pb.check_status()
+    if mode == "fast":
+        redone = pb.last_redo_count()
+        assert (redone > 0) if growth >= 6.0 else (redone >= 0)
     assert torch.isfinite(got.float()).all()
-    assert_close(got, want, f"D={D} growth={growth}")
+    assert_close(got, want, f"D={D} growth={growth} {mode}")
     assert ((lse.cpu() - want_lse).abs() / want_lse.abs().clamp_min(1.0)).max().item() < 2e-3
 
 

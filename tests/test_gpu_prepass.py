@@ -133,7 +133,7 @@ def test_quant_int8_nhd_layout():
 def test_quant_v_fp8(dtype, N, D, smooth):
     B, H = (2, 3) if N < 10000 else (1, 2)
     v = rand((B, H, N, D), dtype, N + 7, offset=0.3) * 2.0
-    v8, vs, vm, v16 = pb.per_channel_fp8(v.to(DEV), smooth_v=smooth, return_f16=True)
+    v8, vs, vm, v16 = pb.per_channel_fp8(v.to(DEV), smooth_v=smooth, return_16=True)
     w8, ws, wm = po.quant_v_fp8(v, smooth=smooth)
     assert torch.equal(vs.cpu(), ws)
     if smooth:
@@ -141,7 +141,7 @@ def test_quant_v_fp8(dtype, N, D, smooth):
     else:
         assert vm is None
     assert torch.equal(v8.cpu().view(torch.uint8), w8.view(torch.uint8))
-    assert torch.equal(v16.cpu(), w8.to(torch.float16))
+    assert torch.equal(v16.cpu(), w8.to(torch.bfloat16))
 
 
 def test_quant_v_fp8_zero_channel_and_nhd():
@@ -194,7 +194,7 @@ def test_fused_prep_equals_separate_passes(dtype, D, family, grid, n_text):
     k8, ks, gkm = pb.prep_qk_int8(k.to(DEV), ids, grid, n_text, tabs, group=64, smooth=True)
     assert torch.equal(gkm.cpu(), km) and torch.equal(k8.cpu(), wk) and torch.equal(ks.cpu(), wks)
     v16, vs, vm, v8 = pb.prep_v_fp8(v.to(DEV), ids, grid, n_text, want_fp8=True)
-    assert torch.equal(v8.cpu().view(torch.uint8), w8.view(torch.uint8)) and torch.equal(v16.cpu(), w8.to(torch.float16))
+    assert torch.equal(v8.cpu().view(torch.uint8), w8.view(torch.uint8)) and torch.equal(v16.cpu(), w8.to(torch.bfloat16))
     assert torch.equal(vs.cpu(), wvs) and torch.equal(vm.cpu(), wvm)
     # NHD input, no fp8 copy
     v16b, _, _, none8 = pb.prep_v_fp8(v.transpose(1, 2).contiguous().to(DEV), ids, grid, n_text, tensor_layout="NHD")

@@ -150,8 +150,53 @@ def test_rope_tables_and_rotation():
     assert cw.dtype == torch.float64
     xw = torch.randn(1, 1, 24, 128).to(torch.bfloat16)
     yw = po.apply_rope_complex(xw, cw, sw)
-    z = torch.view_as_complex(xw.double().unflatten(3, (-1, 2))) * torch.polar(torch.ones_like(cw), torch.atan2(sw, cw))
-    assert (torch.view_as_real(z).flatten(3) - yw.double()).abs().max() < 0.02
+    assert yw.shape == xw.shape and yw.dtype == xw.dtype
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_wan_rotation_equals_the_reference_expression(dtype):
+    """The Wan rotation is pure torch in the reference (paroattention/wan.py:161-164):
+    view_as_complex(x.to(float64).unflatten(3, (-1, 2))) * freqs -> view_as_real -> flatten -> type_as.
+    That expression is evaluated here literally, with freqs = cos + i*sin from the oracle's table, on
+    more than a million elements; the oracle (four separately rounded fp64 products, which the CUDA
+    kernel follows bit for bit) must give the same 16-bit values."""
+    grid, D, H = (6, 15, 12), 128, 9
+    n_img = grid[0] * grid[1] * grid[2]
+    cos, sin = po.rope_full_tables(grid, D, "wan")
+    assert cos.dtype == torch.float64 and cos.shape == (n_img, D // 2)
+    g = torch.Generator().manual_seed(11)
+    x = (torch.randn(1, H, n_img, D, generator=g) * 3).to(dtype)
+    assert x.numel() > 1_000_000
+    freqs = torch.complex(cos, sin).reshape(1, 1, n_img, D // 2)
+
+    def apply_rotary_emb(hidden_states, freqs):          # wan.py:161-164
+        x_rotated = torch.view_as_complex(hidden_states.to(torch.float64).unflatten(3, (-1, 2)))
+        x_out = torch.view_as_real(x_rotated * freqs).flatten(3, 4)
+        return x_out.type_as(hidden_states)
+
+    assert torch.equal(apply_rotary_emb(x, freqs), po.apply_rope_complex(x, cos, sin))
+
+
+def test_wan_rope_table_equals_the_reference_construction():
+    """WanRotaryPosEmbed (wan.py:482-522): per-axis tables of D/2 - 2*(D//6), D//6, D//6 complex
+    frequencies, theta 10000, angles position * theta^(-2i/dim) in fp64 (what diffusers'
+    get_1d_rotary_pos_embed(use_real=False, freqs_dtype=float64) computes: polar(1, outer(pos, freq))),
+    expanded over the (f, h, w) grid and concatenated.  Rebuilt here with plain torch."""
+    grid, D = (3, 4, 5), 128
+    h_dim = w_dim = 2 * (D // 6)
+    t_dim = D - h_dim - w_dim
+    parts = []
+    for dim in (t_dim, h_dim, w_dim):
+        freq = 1.0 / (10000.0 ** (torch.arange(0, dim, 2, dtype=torch.float64)[: dim // 2] / dim))
+        ang = torch.outer(torch.arange(1024, dtype=torch.float64), freq)
+        parts.append(torch.polar(torch.ones_like(ang), ang))
+    f, h, w = grid
+    ff = parts[0][:f].view(f, 1, 1, -1).expand(f, h, w, -1)
+    fh = parts[1][:h].view(1, h, 1, -1).expand(f, h, w, -1)
+    fw = parts[2][:w].view(1, 1, w, -1).expand(f, h, w, -1)
+    freqs = torch.cat([ff, fh, fw], dim=-1).reshape(f * h * w, -1)
+    cos, sin = po.rope_full_tables(grid, D, "wan")
+    assert torch.equal(cos, freqs.real) and torch.equal(sin, freqs.imag)
 
 
 def test_c1_fixture():
