@@ -34,6 +34,7 @@
 // Every wait is bounded: on expiry the CTA records a code in the status words, raises a shared
 // abort flag and unwinds (TMEM freed).
 #include <mutex>
+#include <type_traits>
 
 #include "attn_common.cuh"
 
@@ -374,15 +375,18 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
     // look-up stays inside its array)
     int kb_next = set < n_mine ? min(my_kb(set), p.nb - 1) : 0;
     float ks_next = set < n_mine ? kscale_bh[kb_next] : 0.f;
-    for (int i = set; i < n_mine; i += 2) {   // the two halves only meet in the issuers' queues
+    // One step of this thread's half (the two halves only meet in the issuers' queues).  `first` is a
+    // compile-time tag: the thread's first step, where the fixed-reference walk settles the row's
+    // reference exponent; every later step of that walk is straight-line code from scores to P.
+    auto do_step = [&](const int i, auto first) -> bool {
+      [[maybe_unused]] constexpr bool FIRST = decltype(first)::value;
       const int kb = kb_next;
       const float kscale = ks_next;
       if (i + 2 < n_mine) {   // fetched one step ahead so that the loads are off the critical path
         kb_next = min(my_kb(i + 2), p.nb - 1);
         ks_next = kscale_bh[kb_next];
       }
-      ok = wait_bar(my_sready, i >> 1, 6, i);
-      if (!ok) break;
+      if (!wait_bar(my_sready, i >> 1, 6, i)) return false;
       float f[64];
       {
         uint32_t s[64];
@@ -402,12 +406,12 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
         for (int j = 0; j < 64; ++j) f[j] = __int_as_float((int)s[j] + 0x4B400000);
       }
       const int valid = min(64, p.N - kb * 64);   // columns inside the sequence
-      if (valid < 64) {
+      const float sc = rowscale * kscale;
+      if (!FIXED && valid < 64) {   // (the fixed-reference walk corrects its row sum instead, below)
 #pragma unroll
         for (int j = 0; j < 64; ++j)
           if (j >= valid) f[j] = -INFINITY;
       }
-      const float sc = rowscale * kscale;
       auto row_max = [&]() {   // maximum of the step's scores, in the exponent's units
         float mx4[4] = {f[0], f[1], f[2], f[3]};   // four independent chains of 3-input max
 #pragma unroll
@@ -422,14 +426,14 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
         return (fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) - SCORE_BIAS) * sc;
       };
       float m_new;
-      bool pv_consumed = (i == 0);
+      bool pv_consumed = FIXED ? (FIRST && set == 0) : (i == 0);   // step 0: nothing to wait for
       if constexpr (FIXED) {
-        if (i == 0) {
+        if (FIRST && set == 0) {
           m_ref = row_max() + REF_OFFSET;
           s_mrow[r] = m_ref;
           __syncwarp();
           if (lane == 0) st_release_shared(s_mstep + qd, 1);
-        } else if (i == 1) {   // the other warp set fixed the reference in step 0
+        } else if (FIRST) {   // (step 1) the other warp set fixed the reference in step 0
           bool seen = ld_acquire_shared(s_mstep + qd) != 0;
           if (!seen) {
             const long long t0 = clock64();
@@ -439,8 +443,7 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
           }
           if (!__all_sync(0xffffffffu, seen)) {
             report_timeout(p, abort_flag, 10, i);
-            ok = false;
-            break;
+            return false;
           }
           m_ref = s_mrow[r];
         }
@@ -460,8 +463,7 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
         }
         if (!__all_sync(0xffffffffu, seen)) {
           report_timeout(p, abort_flag, 10, i);
-          ok = false;
-          break;
+          return false;
         }
         m_old = s_mrow[r];
       }
@@ -480,8 +482,7 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
       }
       if (__any_sync(0xffffffffu, resc)) {  // O may only be touched once this half's previous P.V has landed
         pv_consumed = true;
-        ok = wait_bar(prev_pvdone, (i - 1) >> 1, 7, i);
-        if (!ok) break;
+        if (!wait_bar(prev_pvdone, (i - 1) >> 1, 7, i)) return false;
         const float alpha = resc ? ex2_approx(m_old - m_new) : 1.f;
         // (rare, and deliberately not unrolled: unrolled, this loop costs the hot path 19 spilled registers)
 #pragma unroll 1
@@ -513,18 +514,28 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
         }
         // P of this half is rewritten only after the P.V that read its previous contents (the other
         // warp set's step) has finished
-        if (c == 0 && !pv_consumed) ok = wait_bar(prev_pvdone, (i - 1) >> 1, 7, i);
+        if (c == 0 && !pv_consumed && !wait_bar(prev_pvdone, (i - 1) >> 1, 7, i)) return false;
         tmem_st16(tP + lane_off + 16 * c, pk);   // bf16 P: two values per 32-bit column
       }
-      if (!ok) break;
       float sa, sb;
       unpack2(add2(sum2[0], sum2[1]), sa, sb);
       if constexpr (FIXED) redo = redo || !(sa + sb < ROWSUM_LIMIT);   // out of range, or NaN
       l += sa + sb;
+      // Fixed-reference walk: the columns past the end of the sequence were not masked.  Their K rows
+      // arrive as zeros, so each of them scored exactly 0 and contributed the same P to the sum, which
+      // is taken out here; in P.V they meet the zero padding of V.
+      if (FIXED && valid < 64) l -= (float)(64 - valid) * ex2_approx(fmaf(SCORE_BIAS, sc, xoff));
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(my_pready);   // one arrival per warp
+      return true;
+    };
+    if constexpr (FIXED) {
+      if (set < n_mine) ok = do_step(set, std::true_type{});
+      for (int i = set + 2; ok && i < n_mine; i += 2) ok = do_step(i, std::false_type{});
+    } else {
+      for (int i = set; ok && i < n_mine; i += 2) ok = do_step(i, std::false_type{});
     }
 
     // epilogue (the TMEM loads are warp-collective: every lane of the warp executes them, rows past
