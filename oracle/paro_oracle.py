@@ -244,18 +244,20 @@ def quant_int8(x: torch.Tensor, group: int, km: Optional[torch.Tensor] = None,
     return q, scale.contiguous()
 
 
-def quant_v_fp8(v: torch.Tensor, smooth: bool = True, scale_max: float = 448.0):
+def quant_v_fp8(v: torch.Tensor, smooth: bool = True, scale_max: float = 448.0, mean_divisor: Optional[int] = None):
     """Per-channel FP8-e4m3 of V, stored token-contiguous (fused.cu:316-427 with the
     transposed, 64-padded layout of fused.cu:262-313 minus its 16-token shuffle).
     vm = fp32(sum_fp64(v)/N) when smoothing (the reference divides by N rounded up to 16,
     fused.cu:335,381: the true N is used here); amax = max(1e-7, max|v - vm|);
     v_scale = amax/scale_max; v8 = e4m3_rn_satfinite((v - vm) * (scale_max/amax)).
+    mean_divisor: only for comparisons with the reference kernel's own output -- its divisor (N rounded up
+    to 16) instead of N.
     Returns (fp8 [B,H,D,ceil64(N)] zero padded, v_scale [B,H,D] fp32, vm [B,H,D] fp32 or None)."""
     B, H, N, D = v.shape
     vf = v.float()
     vm = None
     if smooth:
-        vm = (v.double().sum(dim=2) / N).float()
+        vm = (v.double().sum(dim=2) / (N if mean_divisor is None else mean_divisor)).float()
         vf = vf - vm.reshape(B, H, 1, D)
     amax = vf.abs().amax(dim=2).clamp_min(1e-7)
     scale = amax / torch.tensor(scale_max)

@@ -14,7 +14,7 @@ import threading
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_PATH = os.path.join(HERE, "libparo_b200.so")
-SOURCES = ("common.cu", "perm_plan.cu", "rope_permute.cu", "quant.cu", "sparse_attn.cu", "sparse_attn_fast.cu")
+SOURCES = ("common.cu", "perm_plan.cu", "rope_permute.cu", "quant.cu", "sparse_attn.cu")
 NVCC_FLAGS = ("-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
               "-Xcompiler", "-fPIC", "-shared")
 

@@ -77,7 +77,7 @@ def sparse_attn_quantized(q_int8, q_scale, k_int8, k_scale, v16, v_scale, vm, pl
     permutation is applied as rows are stored.  Returns O [B,H,N,D] (or [B,N,H,D] when
     out_layout="NHD") and, if asked, LSE [B,H,N] (natural log, in output token order)."""
     _lib.require_cuda(q_int8, k_int8, v16, q_scale, k_scale, v_scale, vm, inv_index)
-    if mode not in ("fast", "exact", "fastT"):
+    if mode not in ("fast", "exact"):
         raise ValueError(f"unknown mode {mode!r}")
     B, H, N, D = q_int8.shape
     nb = (N + 63) // 64
@@ -123,7 +123,7 @@ def sparse_attn_quantized(q_int8, q_scale, k_int8, k_scale, v16, v_scale, vm, pl
             plan.sched_cnt.data_ptr(),
             plan.slices, _lib.ptr(inv_index), int(n_text), out.data_ptr(), _lib.dtype_code(out.dtype),
             ov.stride(0), ov.stride(1), ov.stride(2), _lib.ptr(lse), B, H, N, D, float(sm_scale),
-            {"fast": _lib.ATTN_FAST, "exact": _lib.ATTN_EXACT, "fastT": 2}[mode], _lib.ptr(redo),
+            _lib.ATTN_FAST if mode == "fast" else _lib.ATTN_EXACT, _lib.ptr(redo),
             redo.numel() * 4 if redo is not None else 0, _status_words(dev).data_ptr(), _lib.stream_ptr()))
         if sink is not None:
             ev[1].record()

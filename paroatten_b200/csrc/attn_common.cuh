@@ -1,5 +1,4 @@
-// Pieces shared by the two block-sparse attention kernels (sparse_attn.cu: the walk with an exact
-// running row maximum; sparse_attn_fast.cu: the walk with a fixed per-row reference exponent).
+// Types and small device helpers of the block-sparse attention kernel (sparse_attn.cu).
 #pragma once
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -126,17 +125,5 @@ struct StepGroups {
     which[1] = 1;
   }
 };
-
-// 3-D tensor map over a tensor [d2][d1][d0] of `esize`-byte elements, box [1][box1][box0].
-int make_tensor_map(CUtensorMap* map, CUtensorMapDataType dt, int esize, const void* base, uint64_t d0, uint64_t d1,
-                    uint64_t d2, uint32_t box0, uint32_t box1, CUtensorMapSwizzle swz);
-
-// Launchers (one per file).
-int launch_attn_exact(const int8_t* k8, const uint16_t* v16, const AttnParams& p, int D, int out_dtype, unsigned ctas,
-                      cudaStream_t s);
-int launch_attn_fixed(const int8_t* k8, const uint16_t* v16, const AttnParams& p, int D, int out_dtype, unsigned ctas,
-                      cudaStream_t s);
-int launch_attn_fast(const int8_t* k8, const uint16_t* v16, const AttnParams& p, int D, int out_dtype, unsigned ctas,
-                     cudaStream_t s);
 
 }  // namespace paro

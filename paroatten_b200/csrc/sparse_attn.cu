@@ -1,8 +1,7 @@
-// Block-sparse attention over kept 64x64 blocks for sm_100a: the walk with an EXACT running row
-// maximum (online softmax with rescaling).  paro_sparse_attn first runs the fast walk of
-// sparse_attn_fast.cu on every work item; this kernel then computes the few work items that walk gave
-// back (rows whose scores span more than its exponent range), read from the redo list, and it is the
-// reference point the fast walk is tested against.
+// Block-sparse attention over kept 64x64 blocks for sm_100a.  One kernel, two walks (template flag):
+// the FIXED-REFERENCE walk, which paro_sparse_attn runs on every work item, and the EXACT walk
+// (running row maximum, online softmax with rescaling), which then computes the few work items the
+// first one gave back (rows whose scores span more than its exponent range), read from the redo list.
 //
 // Work item (one CTA): a PAIR of adjacent 64-row q-blocks of one (batch, head), i.e. a 128-row
 // tile -- the native tcgen05.mma M.  The pair walks a schedule built with the plan: first the
@@ -620,7 +619,8 @@ static EncodeTiledFn encode_fn() {
   return fn;
 }
 
-int make_tensor_map(CUtensorMap* map, CUtensorMapDataType dt, int esize, const void* base, uint64_t d0, uint64_t d1,
+// 3-D tensor map over a tensor [d2][d1][d0] of `esize`-byte elements, box [1][box1][box0].
+static int make_tensor_map(CUtensorMap* map, CUtensorMapDataType dt, int esize, const void* base, uint64_t d0, uint64_t d1,
                     uint64_t d2, uint32_t box0, uint32_t box1, CUtensorMapSwizzle swz) {
   EncodeTiledFn fn = encode_fn();
   PARO_REQUIRE(fn != nullptr, PARO_ECUDA, "cuTensorMapEncodeTiled is not available from this driver");
@@ -653,7 +653,7 @@ static int launch_walk(const int8_t* k8, const uint16_t* v16, const AttnParams& 
   return check_launch("sparse_attn_kernel");
 }
 
-int launch_attn_exact(const int8_t* k8, const uint16_t* v16, const AttnParams& p, int D, int out_dtype, unsigned ctas,
+static int launch_attn_exact(const int8_t* k8, const uint16_t* v16, const AttnParams& p, int D, int out_dtype, unsigned ctas,
                       cudaStream_t s) {
   if (D == 128)
     return out_dtype == PARO_F16 ? launch_walk<128, __half, false>(k8, v16, p, ctas, s)
@@ -662,7 +662,7 @@ int launch_attn_exact(const int8_t* k8, const uint16_t* v16, const AttnParams& p
                                : launch_walk<64, __nv_bfloat16, false>(k8, v16, p, ctas, s);
 }
 
-int launch_attn_fixed(const int8_t* k8, const uint16_t* v16, const AttnParams& p, int D, int out_dtype, unsigned ctas,
+static int launch_attn_fixed(const int8_t* k8, const uint16_t* v16, const AttnParams& p, int D, int out_dtype, unsigned ctas,
                       cudaStream_t s) {
   if (D == 128)
     return out_dtype == PARO_F16 ? launch_walk<128, __half, true>(k8, v16, p, ctas, s)
@@ -706,7 +706,7 @@ extern "C" int paro_sparse_attn(const int8_t* q8, const int8_t* k8, const uint16
   PARO_REQUIRE(out_stride_b % 8 == 0 && out_stride_h % 8 == 0 && out_stride_n % 8 == 0 && out_stride_n >= D,
                PARO_EALIGN, "paro_sparse_attn: output strides must be multiples of 8 elements");
   PARO_REQUIRE(sm_scale > 0.f, PARO_EINVAL, "paro_sparse_attn: sm_scale must be positive");
-  PARO_REQUIRE(mode == PARO_ATTN_FAST || mode == PARO_ATTN_EXACT || mode == 2, PARO_EINVAL, "paro_sparse_attn: unknown mode %d", mode);
+  PARO_REQUIRE(mode == PARO_ATTN_FAST || mode == PARO_ATTN_EXACT, PARO_EINVAL, "paro_sparse_attn: unknown mode %d", mode);
   PARO_REQUIRE(mode == PARO_ATTN_EXACT || (redo && redo_bytes >= paro_sparse_attn_redo_bytes(B, H, N)), PARO_ECAP,
                "paro_sparse_attn: the fast walk needs a redo work space of paro_sparse_attn_redo_bytes() bytes");
   AttnParams p;
@@ -722,12 +722,10 @@ extern "C" int paro_sparse_attn(const int8_t* q8, const int8_t* k8, const uint16
   const uint64_t ctas = (uint64_t)B * H * p.npairs;
   PARO_REQUIRE(ctas < (1ull << 31), PARO_ESHAPE, "paro_sparse_attn: too many work items");
   if (mode == PARO_ATTN_EXACT) return launch_attn_exact(k8, v16, p, D, out_dtype, (unsigned)ctas, s);
-  // fast walk over every work item, then the exact walk over the items it gave back (usually none:
+  // fixed-reference walk over every work item, then the exact walk over the items it gave back (usually none:
   // the second launch's CTAs then leave at once)
   PARO_CUDA_OK(cudaMemsetAsync(redo, 0, sizeof(int32_t) * REDO_HEADER, s));
-  if (int rc = mode == 2 ? launch_attn_fast(k8, v16, p, D, out_dtype, (unsigned)ctas, s)
-                         : launch_attn_fixed(k8, v16, p, D, out_dtype, (unsigned)ctas, s))
-    return rc;
+  if (int rc = launch_attn_fixed(k8, v16, p, D, out_dtype, (unsigned)ctas, s)) return rc;
   p.from_list = 1;
   return launch_attn_exact(k8, v16, p, D, out_dtype, (unsigned)ctas, s);
 }

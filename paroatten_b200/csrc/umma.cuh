@@ -53,41 +53,11 @@ __device__ __forceinline__ bool mbar_try_wait_suspend(uint64_t* bar, uint32_t pa
   return ok != 0;
 }
 
-// Up to `polls` attempts in one piece of PTX (no predicate-to-register round trip per attempt).  Each
-// attempt may itself keep the thread suspended for a short, hardware-defined time.
-__device__ __forceinline__ bool mbar_poll(uint64_t* bar, uint32_t parity, uint32_t polls) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p, q;\n\t.reg .u32 n;\n\t"
-      "mov.u32 n, %3;\n\t"
-      "POLL_%=:\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "@p bra DONE_%=;\n\t"
-      "sub.u32 n, n, 1;\n\t"
-      "setp.ne.u32 q, n, 0;\n\t"
-      "@q bra POLL_%=;\n\t"
-      "DONE_%=:\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity), "r"(polls)
-      : "memory");
-  return ok != 0;
-}
-
 // Waits for the phase with the given parity to complete, for at most `limit_cycles` of the SM
 // clock; also gives up as soon as *abort_flag (shared memory) is non-zero.  Returns false on
 // expiry so that the caller can unwind instead of hanging the GPU.
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                                   long long limit_cycles) {
-#ifdef PARO_POLL_ASM
-  if (mbar_poll(bar, parity, 32)) return true;
-  const long long t0 = clock64();
-  do {
-    if (*abort_flag) return false;
-    if (mbar_poll(bar, parity, 64)) return true;
-  } while (clock64() - t0 <= limit_cycles);
-  return false;
-#else
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   while (!mbar_try_wait_suspend(bar, parity, 20000u)) {
@@ -95,7 +65,6 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
     if (clock64() - t0 > limit_cycles) return false;
   }
   return true;
-#endif
 }
 
 // The same without an abort flag: used by a role that is already leaving and only has to see its own
@@ -258,27 +227,6 @@ __device__ __forceinline__ void mma_f16_ts_masked(uint32_t d_tmem, uint32_t a_tm
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %6, %7, %8}, p;\n\t}"
       ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(m0), "r"(m1), "r"(m2), "r"(m3)
-      : "memory");
-}
-// D[tmem] (+)= A[smem] * B[smem]^T, 16-bit float operands (formats in the instruction descriptor), fp32 accumulator.
-__device__ __forceinline__ void mma_f16_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                           uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// int8 operands both from shared memory, with a 128-bit mask of accumulator lanes that are NOT written.
-__device__ __forceinline__ void mma_i8_ss_masked(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                                 uint32_t accumulate, uint32_t m0, uint32_t m1, uint32_t m2,
-                                                 uint32_t m3) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(m0), "r"(m1), "r"(m2), "r"(m3)
       : "memory");
 }
 // Arrives once on `bar` when every tcgen05.mma issued so far by this thread has completed.
