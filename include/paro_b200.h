@@ -196,6 +196,18 @@ int paro_plan_fill(const uint8_t* mask, int slices, int nbq, int nbk,
 int paro_plan_schedule(const int32_t* pair_ptr, const int32_t* pair_ent, int slices, int nbq, int nbk,
                        uint32_t* sched, int32_t* sched_cnt, paro_stream_t stream);
 
+/* Checks walk lists that did not come from paro_plan_schedule in this process (read from a file, built
+ * by other code) before paro_sparse_attn follows them: pair_ptr starts at 0, is monotone and stays within
+ * sched_len entries; each q-block's step count fits its pair's slots (and is 0 for a q-block past the end);
+ * every k-block id inside a q-block's steps is < nbk and every entry past them is the 0xFFFF filler;
+ * shared steps come first and the k-blocks of each section ascend strictly (so none repeats).
+ * report: 4 device words of scratch.  Synchronises `stream`; returns PARO_OK or PARO_EINVAL with the first
+ * fault in paro_last_error().  The reference shape-checks its mask argument in the same spirit
+ * (csrc/qattn/qk_int_sv_f16_cuda_sm80.cu:1034-1038). */
+int paro_plan_validate(const int32_t* pair_ptr, const uint32_t* sched, const int32_t* sched_cnt,
+                       int slices, int nbq, int nbk, int64_t sched_len, int32_t* report,
+                       paro_stream_t stream);
+
 /* ---- attention ------------------------------------------------------------------------- */
 
 /* Block-sparse attention over the kept 64x64 blocks with the inverse permutation fused
@@ -233,6 +245,18 @@ int paro_sparse_attn(const int8_t* q8, const int8_t* k8, const uint16_t* v16,
                      float* lse, int B, int H, int N, int D, float sm_scale, int mode,
                      int32_t* redo, size_t redo_bytes,
                      int32_t* status, paro_stream_t stream);
+
+/* Merges two partial results of paro_sparse_attn computed over DISJOINT sets of key blocks (for
+ * instance the two halves of a sequence held by two ranks) into the result over their union:
+ * lse = log(exp(lse_a) + exp(lse_b)), out = o_a * exp(lse_a - lse) + o_b * exp(lse_b - lse), fp32 math,
+ * out in the tensors' dtype.  A row whose LSE is -inf on one side (no kept block there) takes the other
+ * side unchanged.  o_a, o_b, out: [B,H,N,D] through the same element strides (out may alias o_a or o_b);
+ * lse_*: fp32 [B,H,N] contiguous, natural log; lse_out may be NULL.  This is the consumer of the LSE
+ * output that the reference returns "for cases like Ring Attention" (paroattention/core.py:55-57,
+ * kernel qk_int_sv_f16_cuda_sm80.cu:711-723) and leaves to the caller. */
+int paro_merge_attn_states(const void* o_a, const float* lse_a, const void* o_b, const float* lse_b,
+                           void* out, float* lse_out, int dtype, int B, int H, int N, int D,
+                           int64_t stride_b, int64_t stride_h, int64_t stride_n, paro_stream_t stream);
 
 /* Synchronises `stream`, copies the 4 status words to host_out (host pointer, may be NULL)
  * and returns PARO_OK, PARO_ETIMEOUT (word 0 non-zero) or PARO_ECUDA.  After a timeout word 1 names

@@ -224,15 +224,16 @@ def quant_int8(x: torch.Tensor, group: int, km: Optional[torch.Tensor] = None,
     x = float(in) [- float(km)] [* fold_scale]; rows >= N count as 0;
     amax = max(1e-7, max|x|) over group*D values; scale = amax/127;
     q = sat_s8(round_half_even(x * (127/amax))).  Groups tile the sequence padded up to a
-    multiple of 64 tokens, so `group`=32 yields 2 scales per 64-token block (quant.py:169).
-    Returns (int8 [B,H,N,D], fp32 scale [B,H,ceil(N/64)*(64/group)])."""
+    multiple of max(64, group) tokens, so `group`=32 yields 2 scales per 64-token block (quant.py:169).
+    Returns (int8 [B,H,N,D], fp32 scale [B,H,ceil(N/64)*(64/group)] (group <= 64) or [B,H,ceil(N/group)])."""
     B, H, N, D = x.shape
     xf = x.float()
     if km is not None:
         xf = xf - km.float().reshape(B, H, 1, D)
     if fold_scale is not None:
         xf = xf * torch.tensor(fold_scale, dtype=torch.float32)
-    npad = (N + 63) // 64 * 64
+    tile = max(64, group)
+    npad = (N + tile - 1) // tile * tile
     if npad != N:
         xf = torch.cat([xf, torch.zeros(B, H, npad - N, D)], dim=2)
     g = xf.reshape(B, H, npad // group, group * D)
@@ -350,7 +351,8 @@ def sparse_attention(q_i8, q_scale, k_i8, k_scale, v8, v_scale, vm, mask, sm_sca
     nb = (N + 63) // 64
     m = mask.reshape(-1, nb, nb).bool()
     out = torch.zeros(B, H, N, D, dtype=out_dtype)
-    lse = torch.zeros(B, H, N, dtype=torch.float32) if return_lse else None
+    # a row without a kept block has an empty sum: output 0, LSE = log 0 = -inf
+    lse = torch.full((B, H, N), float("-inf"), dtype=torch.float32) if return_lse else None
     c = torch.tensor(sm_scale, dtype=torch.float32) * torch.tensor(LOG2E, dtype=torch.float32)
     per64 = 64 // q_group
     for b in range(B):
@@ -383,13 +385,47 @@ def sparse_attention(q_i8, q_scale, k_i8, k_scale, v8, v_scale, vm, mask, sm_sca
     return (out, lse) if return_lse else out
 
 
+def merge_attention_states(o_a, lse_a, o_b, lse_b):
+    """Two partial attention results over disjoint key sets -> the result over their union (what the
+    reference returns the LSE for, core.py:55-57): lse = log(e^lse_a + e^lse_b),
+    o = o_a * e^(lse_a - lse) + o_b * e^(lse_b - lse) in fp32, rounded to o_a's dtype.  o_*: [B,H,N,D];
+    lse_*: [B,H,N] natural log, -inf where a side kept no block for the row (that side is then ignored)."""
+    m = torch.maximum(lse_a, lse_b)
+    safe = torch.where(torch.isfinite(m), m, torch.zeros_like(m))
+    ea, eb = torch.exp(lse_a - safe), torch.exp(lse_b - safe)
+    ssum = ea + eb
+    wa = torch.where(ssum > 0, ea / ssum.clamp_min(1e-38), torch.zeros_like(ea)).unsqueeze(-1)
+    wb = torch.where(ssum > 0, eb / ssum.clamp_min(1e-38), torch.zeros_like(eb)).unsqueeze(-1)
+    va = torch.where(wa != 0, wa * o_a.float(), torch.zeros_like(o_a, dtype=torch.float32))
+    vb = torch.where(wb != 0, wb * o_b.float(), torch.zeros_like(o_b, dtype=torch.float32))
+    lse = torch.where(ssum > 0, safe + torch.log(ssum.clamp_min(1e-38)), torch.full_like(m, float("-inf")))
+    return (va + vb).to(o_a.dtype), lse
+
+
+def apply_empty_heads(mask, empty, n_text_blocks=0):
+    """The video-to-video blocks of the heads flagged in `empty` ([H] bool) switched off; text rows and
+    columns stay (the mask multiply of example/pipeline_cogvideox.py:76-77, before its text padding)."""
+    if empty is None:
+        return mask
+    out = mask.clone()
+    t = int(n_text_blocks)
+    for h in torch.as_tensor(empty).bool().nonzero().flatten().tolist():
+        out[..., h, t:, t:] = False
+    return out
+
+
 def paro_attention(q, k, v, order_ids, mask, grid, n_text=0, rope=None, sm_scale=None,
-                   smooth_k=True, smooth_v=True, q_group=32, return_lse=False, q_norm=None, k_norm=None):
+                   smooth_k=True, smooth_v=True, q_group=32, return_lse=False, q_norm=None, k_norm=None,
+                   empty=None, empty_mode="zero"):
     """The composed path as the processors run it (cogvideox.py:167-227): RoPE on Q,K ->
     permute Q,K,V -> INT8 Q (per 32 rows), INT8 K (per 64 rows, mean-smoothed), FP8 V ->
     block-sparse attention -> inverse permute.  `rope` = None | ("real"|"complex", cos, sin)
-    with per-token tables [F*H*W, D/2]; q_norm / k_norm as in `apply_qk_norm` (applied first)."""
+    with per-token tables [F*H*W, D/2]; q_norm / k_norm as in `apply_qk_norm` (applied first).
+    empty ([H] bool, the permute plan's 'empty' flags; bench/check.py:116-128): "zero" removes the flagged
+    heads' video-to-video blocks; "uniform" (n_text == 0 only) sets their output to the mean of V over the
+    tokens (fp64 sum, rounded to fp32, then to the output dtype)."""
     D = q.shape[-1]
+    mask = apply_empty_heads(mask, empty, (n_text + 63) // 64)
     if sm_scale is None:
         sm_scale = D ** -0.5
     q, k = apply_qk_norm(q, q_norm), apply_qk_norm(k, k_norm)
@@ -406,11 +442,17 @@ def paro_attention(q, k, v, order_ids, mask, grid, n_text=0, rope=None, sm_scale
     v8, vs, vm = quant_v_fp8(vp, smooth=smooth_v)
     res = sparse_attention(q8, qs, k8, ks, v8, vs, vm, mask, sm_scale, q_group=q_group,
                            out_dtype=q.dtype, return_lse=return_lse)
+    o, lse = res if return_lse else (res, None)
+    o = inverse_permute_tokens(o, order_ids, grid, n_text)
+    if empty is not None and empty_mode == "uniform":
+        assert n_text == 0, "uniform treatment is defined for sequences without text tokens"
+        hs = torch.as_tensor(empty).bool().nonzero().flatten()
+        mean_v = (v.double().sum(dim=2) / v.shape[2]).float()          # [B,H,D]
+        o[:, hs] = mean_v[:, hs].to(o.dtype).unsqueeze(2).expand(-1, -1, o.shape[2], -1)
     if return_lse:
-        o, lse = res
         lse = inverse_permute_tokens(lse.unsqueeze(-1), order_ids, grid, n_text).squeeze(-1)
-        return inverse_permute_tokens(o, order_ids, grid, n_text), lse
-    return inverse_permute_tokens(res, order_ids, grid, n_text)
+        return o, lse
+    return o
 
 
 # --------------------------------------------------------------------------- metrics

@@ -14,7 +14,7 @@ import threading
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_PATH = os.path.join(HERE, "libparo_b200.so")
-SOURCES = ("common.cu", "perm_plan.cu", "rope_permute.cu", "quant.cu", "sparse_attn.cu")
+SOURCES = ("common.cu", "perm_plan.cu", "rope_permute.cu", "quant.cu", "sparse_attn.cu", "attn_aux.cu")
 NVCC_FLAGS = ("-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
               "-Xcompiler", "-fPIC", "-shared")
 
@@ -109,6 +109,8 @@ SIGNATURES = {
     "paro_sparse_attn": (_i32, [_vp, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _vp, _i32, _vp, _i32,
                                 _i64, _i64, _i64, _vp, _i32, _i32, _i32, _i32, _f32, _i32, _vp, _sz, _vp, _vp]),
     "paro_status_poll": (_i32, [_vp, _vp, _vp]),
+    "paro_plan_validate": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _i64, _vp, _vp]),
+    "paro_merge_attn_states": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i64, _i64, _i64, _vp]),
 }
 
 

@@ -7,12 +7,13 @@ import torch
 import torch.nn.functional as F
 
 from . import _lib
-from .plan import CompactPlan, PermutePlan, PlanStore, SparsePlan, compact_plan, perm_index
+from .plan import (CompactPlan, PermutePlan, PlanStore, SparsePlan, apply_empty_heads, compact_plan, perm_index)
 from .quant import (_hnd, _quant_int8, channel_mean, per_channel_fp8, per_warp_int8, per_block_int8, prep_qk_int8,
                     prep_v_fp8)
 from .rope import RopeTables, rope_permute
 
 _status = {}
+_status_mirror = {}   # device index -> pinned host copy of the status words, refreshed after every launch
 _redo = {}       # (device index, stream handle) -> work space of the fast walk
 _timing_sink = None  # optional list receiving (start, end) CUDA events around each attention launch
 
@@ -54,14 +55,34 @@ def last_redo_count(device=None) -> int:
 
 def check_status(device=None) -> None:
     """Synchronises the current stream and raises if an attention launch on `device` gave up a
-    bounded wait (the launch's output is then invalid)."""
+    bounded wait (the launch's output is then invalid).  The status words are cleared when it raises."""
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
     words = _status_words(device)
     with torch.cuda.device(device):
         rc = _lib.lib().paro_status_poll(words.data_ptr(), None, _lib.stream_ptr())
         if rc != _lib.PARO_OK:
             words.zero_()
+            key = device.index if device.index is not None else torch.cuda.current_device()
+            if key in _status_mirror:
+                _status_mirror[key].zero_()
         _lib.check(rc)
+
+
+def _mirror(device: torch.device) -> torch.Tensor:
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    if key not in _status_mirror:
+        _status_mirror[key] = torch.zeros(4, dtype=torch.int32).pin_memory()
+    return _status_mirror[key]
+
+
+def _raise_if_earlier_launch_failed(device: torch.device) -> None:
+    """Every attention launch is followed by an asynchronous copy of the status words into pinned host
+    memory; each new call looks at that copy first (no synchronisation).  A launch that gave up a wait
+    therefore stops the caller at the next attention call at the latest, instead of every later launch
+    returning at once and leaving its output unwritten."""
+    m = _mirror(device)
+    if int(m[0]) != 0:
+        check_status(device)      # synchronises, clears the words and raises with the waiter's position
 
 
 def sparse_attn_quantized(q_int8, q_scale, k_int8, k_scale, v16, v_scale, vm, plan: CompactPlan, sm_scale: float,
@@ -104,6 +125,7 @@ def sparse_attn_quantized(q_int8, q_scale, k_int8, k_scale, v16, v_scale, vm, pl
                                   or not inv_index.is_contiguous()):
         raise ValueError(f"inv_index must be contiguous int32 [H, N - n_text] = [{H}, {N - n_text}]")
     dev = q_int8.device
+    _raise_if_earlier_launch_failed(dev)
     with torch.cuda.device(dev):
         if out is None:
             shape = (B, H, N, D) if out_layout == "HND" else (B, N, H, D)
@@ -128,7 +150,38 @@ def sparse_attn_quantized(q_int8, q_scale, k_int8, k_scale, v16, v_scale, vm, pl
         if sink is not None:
             ev[1].record()
             sink.append(ev)
+        _mirror(dev).copy_(_status_words(dev), non_blocking=True)
     return (out, lse) if return_lse else out
+
+
+def merge_attention_states(o_a: torch.Tensor, lse_a: torch.Tensor, o_b: torch.Tensor, lse_b: torch.Tensor,
+                           tensor_layout: str = "HND", out: Optional[torch.Tensor] = None):
+    """Combines two partial attention results over DISJOINT sets of key blocks -- (o_a, lse_a) and
+    (o_b, lse_b) from calls with return_lse=True -- into the result over their union: the consumer of the
+    LSE that the reference returns "for cases like Ring Attention" (paroattention/core.py:55-57).
+    o_*: [B,H,N,D] ("HND") or [B,N,H,D] ("NHD"), fp16/bf16; lse_*: fp32 [B,H,N], natural log, -inf for rows
+    without a kept block.  Returns (o, lse)."""
+    _lib.require_cuda(o_a, o_b, lse_a, lse_b)
+    if o_a.shape != o_b.shape or o_a.dtype != o_b.dtype or o_a.stride() != o_b.stride():
+        raise ValueError("o_a and o_b must have the same shape, dtype and strides")
+    va = o_a if tensor_layout == "HND" else o_a.transpose(1, 2)
+    vb = o_b if tensor_layout == "HND" else o_b.transpose(1, 2)
+    B, H, N, D = va.shape
+    if va.stride(-1) != 1:
+        raise ValueError("last dimension must be contiguous")
+    for t in (lse_a, lse_b):
+        if t.dtype != torch.float32 or tuple(t.shape) != (B, H, N) or not t.is_contiguous():
+            raise ValueError("lse_a / lse_b must be contiguous fp32 [B,H,N]")
+    with torch.cuda.device(o_a.device):
+        if out is None:
+            out = torch.empty_like(o_a)
+        elif out.shape != o_a.shape or out.dtype != o_a.dtype or out.stride() != o_a.stride():
+            raise ValueError("out must match o_a")
+        lse = torch.empty(B, H, N, dtype=torch.float32, device=o_a.device)
+        _lib.check(_lib.lib().paro_merge_attn_states(
+            o_a.data_ptr(), lse_a.data_ptr(), o_b.data_ptr(), lse_b.data_ptr(), out.data_ptr(), lse.data_ptr(),
+            _lib.dtype_code(o_a.dtype), B, H, N, D, va.stride(0), va.stride(1), va.stride(2), _lib.stream_ptr()))
+    return out, lse
 
 
 def _pad_head_dim(*ts):
@@ -212,7 +265,7 @@ def paro_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, permute_pl
                    i_block: int = 0, i_timestep: int = 0, grid_fhw: Tuple[int, int, int], n_text: int = 0,
                    rope: Optional[RopeTables] = None, tensor_layout: str = "HND", sm_scale: Optional[float] = None,
                    smooth_k: bool = True, smooth_v: bool = True, return_lse: bool = False,
-                   q_norm=None, k_norm=None, attn_mode: str = "fast"):
+                   q_norm=None, k_norm=None, attn_mode: str = "fast", empty_head_mode: str = "zero"):
     """The whole path of one self-attention layer, as the reference processors compose it
     (cogvideox.py:161-227): q, k, v in NATURAL token order ->
     [q_norm / k_norm (rope.QKNorm): the processors' norm_q / norm_k, applied to every token as it is read]
@@ -221,9 +274,16 @@ def paro_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, permute_pl
     -> block-sparse attention over the kept blocks of sparse_plan[i_timestep, i_block]
     -> output rows stored back in natural token order.
 
-    permute_plan: PermutePlan, or the reference's dict {'permute': [L,H]}, or int order ids [H].
+    permute_plan: PermutePlan, or the reference's dict {'permute': [L,H], 'empty': [L,H]}, or int order ids [H].
     sparse_plan: SparsePlan, the reference's [T,L,H,nb,nb] tensor, a mask [H,nb,nb] / [B,H,nb,nb],
-    or a CompactPlan."""
+    or a CompactPlan.
+    Heads flagged in permute_plan['empty'][i_block] (the reference computes the flags and acts on them in
+    bench/check.py:116-128; its pipeline's mask multiply is commented out, example/pipeline_cogvideox.py:76-77):
+    empty_head_mode "zero" drops every video-to-video block of such a head from the walk (text rows and
+    columns stay; a head without text keeps nothing and yields zeros); "uniform" -- sequences without text
+    only -- makes the head attend uniformly, i.e. its output is the mean of V over the tokens.  Masks handed
+    over already compacted (CompactPlan, SparsePlan, PlanStore) must have had plan.apply_empty_heads applied
+    by the caller."""
     _lib.require_cuda(q, k, v)
     if not (q.dtype == k.dtype == v.dtype) or q.dtype not in (torch.float16, torch.bfloat16):
         raise ValueError("q, k, v must share dtype fp16 or bf16")
@@ -235,20 +295,31 @@ def paro_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, permute_pl
         sm_scale = head_dim_og ** -0.5
     dev = q.device
     with torch.cuda.device(dev):
+        empty = None
         if isinstance(permute_plan, PermutePlan):
             orders, index = permute_plan.orders(i_block), permute_plan.index(i_block)
+            empty = permute_plan.empty(i_block)
         else:
             ids = permute_plan["permute"][i_block] if isinstance(permute_plan, dict) else permute_plan
             orders = torch.as_tensor(ids).to(dev, torch.int32).contiguous()
             index = perm_index(orders, grid, dev)
+            if isinstance(permute_plan, dict) and permute_plan.get("empty") is not None:
+                empty = torch.as_tensor(permute_plan["empty"][i_block]).to(dev).bool()
+        if empty is not None and not bool(empty.any()):
+            empty = None
+        if empty_head_mode not in ("zero", "uniform"):
+            raise ValueError(f"unknown empty_head_mode {empty_head_mode!r}")
+        if empty is not None and empty_head_mode == "uniform" and n_text > 0:
+            raise NotImplementedError("empty_head_mode='uniform' is defined for sequences without text tokens")
+        n_text_blocks = (n_text + 63) // 64
         if isinstance(sparse_plan, (SparsePlan, PlanStore)):
             plan = sparse_plan.get(i_timestep, i_block)
         elif isinstance(sparse_plan, CompactPlan):
             plan = sparse_plan
         elif sparse_plan.dim() == 5:
-            plan = compact_plan(sparse_plan[i_timestep, i_block].to(dev))
+            plan = compact_plan(apply_empty_heads(sparse_plan[i_timestep, i_block].to(dev), empty, n_text_blocks))
         else:
-            plan = compact_plan(sparse_plan.to(dev))
+            plan = compact_plan(apply_empty_heads(sparse_plan.to(dev), empty, n_text_blocks))
         # Q and V: the quantisers read the natural-order tensors through the RoPE + reordering front end
         # (no reordered 16-bit copy).  Smoothed K needs the mean of the rotated values first; rotating
         # twice costs more than writing the rotated copy once, so K keeps the two-step form.
@@ -263,6 +334,19 @@ def paro_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, permute_pl
         res = sparse_attn_quantized(q8, qs, k8, ks, v16, vs, vm, plan, sm_scale, out_dtype=q.dtype, q_group=32,
                                     inv_index=index, n_text=n_text, return_lse=return_lse, out_layout=tensor_layout,
                                     mode=attn_mode)
+        if empty is not None and empty_head_mode == "uniform":
+            # uniform attention over all N tokens: O = mean of V (the channel mean the V quantiser produced,
+            # or one reduction when smoothing is off); LSE of N equal scores of value 0
+            o_, _ = res if return_lse else (res, None)
+            mean_v = vm if vm is not None else channel_mean(v, tensor_layout, out_dtype=torch.float32)
+            hsel = empty.nonzero().flatten()
+            fill = mean_v[:, hsel].to(o_.dtype)                       # [B, n_empty, D]
+            if tensor_layout == "HND":
+                o_[:, hsel] = fill.unsqueeze(2).expand(-1, -1, o_.shape[2], -1)
+            else:
+                o_[:, :, hsel] = fill.unsqueeze(1).expand(-1, o_.shape[1], -1, -1)
+            if return_lse:
+                res[1][:, hsel] = float(torch.log(torch.tensor(float(q.shape[2 if tensor_layout == "HND" else 1]))))
     o, lse = res if return_lse else (res, None)
     o = o[..., :head_dim_og]
     return (o, lse) if return_lse else o

@@ -66,9 +66,46 @@ class CompactPlan:
         return int((self.pair_ent & 3).eq(3).sum().item()) if self.pair_ent is not None else -1
 
 
-def compact_plan(mask: torch.Tensor) -> CompactPlan:
-    """mask: bool/uint8 [..., nbq, nbk] on the GPU (leading dims are flattened to slices)."""
+def apply_empty_heads(mask: torch.Tensor, empty: Optional[torch.Tensor], n_text_blocks: int = 0) -> torch.Tensor:
+    """mask [..., H, nbq, nbk] with the video-to-video blocks of the heads flagged in `empty` (bool [H])
+    switched off; the first n_text_blocks rows and columns (text tokens) stay as they are.  This is the mask
+    multiply of the reference's pipeline set-up (example/pipeline_cogvideox.py:76-77) applied before the text
+    padding.  Returns `mask` itself when no head is flagged."""
+    if empty is None:
+        return mask
+    empty = torch.as_tensor(empty).to(mask.device).bool()
+    if empty.numel() != mask.shape[-3]:
+        raise ValueError(f"empty-head flags must hold one entry per head ({mask.shape[-3]})")
+    if not bool(empty.any()):
+        return mask
+    out = mask.clone()
+    t = int(n_text_blocks)
+    region = out[..., t:, t:]
+    region[..., empty, :, :] = False if out.dtype == torch.bool else 0
+    return out
+
+
+def validate_plan(plan: "CompactPlan") -> None:
+    """Checks the walk lists of a plan on the GPU (paro_plan_validate) and raises ValueError naming the first
+    fault.  Lists produced by compact_plan in this process are correct by construction; this is for lists
+    that come from a file or from other code.  Synchronises the current stream."""
+    _lib.require_cuda(plan.pair_ptr, plan.sched, plan.sched_cnt)
+    dev = plan.pair_ptr.device
+    with torch.cuda.device(dev):
+        report = torch.zeros(4, dtype=torch.int32, device=dev)
+        _lib.check(_lib.lib().paro_plan_validate(
+            plan.pair_ptr.data_ptr(), plan.sched.data_ptr(), plan.sched_cnt.data_ptr(), plan.slices, plan.nbq, plan.nbk,
+            plan.sched.numel(), report.data_ptr(), _lib.stream_ptr()))
+
+
+def compact_plan(mask: torch.Tensor, validate: Optional[bool] = None) -> CompactPlan:
+    """mask: bool/uint8 [..., nbq, nbk] on the GPU (leading dims are flattened to slices).
+    validate: run validate_plan on the result (default: only when the environment variable
+    PARO_DEBUG_PLANS is set to a non-empty value other than 0)."""
     _lib.require_cuda(mask)
+    if validate is None:
+        import os
+        validate = os.environ.get("PARO_DEBUG_PLANS", "0") not in ("", "0")
     if mask.dim() < 2:
         raise ValueError("mask must have at least 2 dimensions")
     nbq, nbk = int(mask.shape[-2]), int(mask.shape[-1])
@@ -91,8 +128,11 @@ def compact_plan(mask: torch.Tensor) -> CompactPlan:
         sched_cnt = torch.empty(slices * npairs, 2, dtype=torch.int32, device=m.device)
         _lib.check(L.paro_plan_schedule(pair_ptr.data_ptr(), pair_ent.data_ptr(), slices, nbq, nbk, sched.data_ptr(),
                                         sched_cnt.data_ptr(), s))
-    return CompactPlan(slices, nbq, nbk, row_ptr, cols[:kept], pair_ptr, pair_ent[:tiles], kept, tiles,
+    plan = CompactPlan(slices, nbq, nbk, row_ptr, cols[:kept], pair_ptr, pair_ent[:tiles], kept, tiles,
                        sched[:tiles], sched_cnt)
+    if validate:
+        validate_plan(plan)
+    return plan
 
 
 class SparsePlan:
@@ -121,6 +161,7 @@ class PermutePlan:
 
     def __init__(self, permute_plan, grid: Tuple[int, int, int], device=None):
         self.permute = permute_plan["permute"] if isinstance(permute_plan, dict) else permute_plan
+        self._empty = permute_plan.get("empty") if isinstance(permute_plan, dict) else None
         self.grid = tuple(int(g) for g in grid)
         self.device = torch.device(device) if device is not None else torch.device("cuda")
         self._orders: Dict[int, torch.Tensor] = {}
@@ -130,6 +171,12 @@ class PermutePlan:
         if i_block not in self._orders:
             self._orders[i_block] = torch.as_tensor(self.permute[i_block]).to(self.device, torch.int32).contiguous()
         return self._orders[i_block]
+
+    def empty(self, i_block: int) -> Optional[torch.Tensor]:
+        """bool [H] flags of the layer's empty heads (the plan's 'empty' entry), or None."""
+        if self._empty is None:
+            return None
+        return torch.as_tensor(self._empty[i_block]).to(self.device).bool()
 
     def index(self, i_block: int) -> torch.Tensor:
         if i_block not in self._index:
@@ -147,7 +194,10 @@ class PlanStore:
     the compacted lists are 4 bytes per KEPT block (9 MB at density 0.2).  `get` has the call shape of
     `SparsePlan.get`, so a processor can use either."""
 
-    def __init__(self, sparse: Optional[torch.Tensor] = None, device=None, _lists=None):
+    def __init__(self, sparse: Optional[torch.Tensor] = None, device=None, _lists=None, empty: Optional[torch.Tensor] = None,
+                 n_text_blocks: int = 0):
+        """empty: the permute plan's 'empty' flags, bool [L, H]; flagged heads lose their video-to-video
+        blocks (apply_empty_heads) before compaction."""
         self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
         self.kept = {}
         if _lists is not None:
@@ -160,7 +210,8 @@ class PlanStore:
             self.lists = {}
             for t in range(T):
                 for l in range(L):
-                    p = compact_plan(sparse[t, l].to(self.device))
+                    p = compact_plan(apply_empty_heads(sparse[t, l].to(self.device),
+                                                       None if empty is None else empty[l], n_text_blocks))
                     self.lists[(t, l)] = tuple(x.cpu().pin_memory() for x in (p.pair_ptr, p.sched, p.sched_cnt))
                     self.kept[(t, l)] = p.kept_blocks
         cap = max(c.numel() for _, c, _ in self.lists.values())
@@ -203,6 +254,9 @@ class PlanStore:
         """The slice's plan, usable on the current stream (waits for its copy if one is in flight).
         It stays valid until the second `prefetch` after this call."""
         key = (int(i_timestep), int(i_block))
+        if key not in self.lists:
+            raise KeyError(f"the plan store holds no slice for (timestep bin {key[0]}, layer {key[1]}); "
+                           f"it has {self.meta['T']} bins x {self.meta['L']} layers")
         if key not in self._slot:
             self.prefetch(*key)
         b, ev = self._slot[key]
@@ -224,4 +278,20 @@ class PlanStore:
         key = lambda k: tuple(int(x) for x in k.split(","))
         lists = {key(k): tuple(x.pin_memory() for x in v) for k, v in blob["lists"].items()}
         kept = {key(k): int(n) for k, n in blob.get("kept", {}).items()}
-        return cls(device=device, _lists=(blob["meta"], lists, kept))
+        store = cls(device=device, _lists=(blob["meta"], lists, kept))
+        store.validate()          # lists from a file go to the kernel only after the device-side check
+        return store
+
+    def validate(self) -> None:
+        """Runs validate_plan on every stored slice (uploads each once); raises ValueError on the first fault."""
+        m = self.meta
+        prows = m["H"] * ((m["nbq"] + 1) // 2)
+        for key_, (pair_ptr, sched, sched_cnt) in sorted(self.lists.items()):
+            if pair_ptr.numel() != prows + 1 or sched_cnt.numel() != 2 * prows or pair_ptr.dtype != torch.int32:
+                raise ValueError(f"sparse plan slice {key_}: list sizes do not match H={m['H']}, nbq={m['nbq']}")
+            dev_lists = [x.to(self.device) for x in (pair_ptr, sched, sched_cnt)]
+            try:
+                validate_plan(CompactPlan(m["H"], m["nbq"], m["nbk"], None, None, dev_lists[0], None, 0, sched.numel(),
+                                          dev_lists[1], dev_lists[2]))
+            except ValueError as e:
+                raise ValueError(f"sparse plan slice {key_}: {e}") from None

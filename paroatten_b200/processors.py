@@ -18,9 +18,9 @@ from typing import Optional
 import torch
 
 from . import _lib
-from .core import paro_attention
+from .core import check_status, paro_attention
 from .plan import PermutePlan, PlanStore, SparsePlan
-from .rope import QKNorm, RopeTables, rope_tables
+from .rope import QKNorm, RopeTables, rope_tables, tables_from_embedding
 
 
 class _ProcessorBase:
@@ -35,6 +35,7 @@ class _ProcessorBase:
         self.i_block = 0
         self.i_timestep = 0
         self.smooth_k = True
+        self.empty_head_mode = "zero"  # what to do with heads flagged in permute_plan['empty'] (see paro_attention)
         self.fuse_qk_norm = True      # fold norm_q / norm_k into the RoPE + reorder + quantise passes
         self._rope_cache = {}
         self._pplan = None
@@ -56,10 +57,20 @@ class _ProcessorBase:
             self._splan = src if isinstance(src, (SparsePlan, PlanStore)) else SparsePlan(src, device)
         return self._pplan, self._splan
 
-    def _rope(self, head_dim, device) -> RopeTables:
-        key = (head_dim, tuple(self.grid_fhw), str(device))
+    def _rope(self, head_dim, device, emb=None) -> RopeTables:
+        """Tables for the fused rotation.  `emb` is the rotary embedding the pipeline passed in: the angles
+        are taken from it (rope.tables_from_embedding; cached per tensor), as the reference applies the
+        embedding it is given (cogvideox.py:167-172, wan.py:161-167).  With emb=True the tables are built
+        for grid_fhw with theta 10000."""
+        if emb is None or emb is True:
+            key = (head_dim, tuple(self.grid_fhw), str(device))
+            if key not in self._rope_cache:
+                self._rope_cache[key] = rope_tables(self.grid_fhw, head_dim, self.rope_family, device=device)
+            return self._rope_cache[key]
+        first = emb[0] if isinstance(emb, (tuple, list)) else emb
+        key = ("emb", first.data_ptr(), tuple(first.shape), first._version, head_dim, tuple(self.grid_fhw), str(device))
         if key not in self._rope_cache:
-            self._rope_cache[key] = rope_tables(self.grid_fhw, head_dim, self.rope_family, device=device)
+            self._rope_cache[key] = tables_from_embedding(emb, self.grid_fhw, head_dim, self.rope_family, device=device)
         return self._rope_cache[key]
 
     def _norms(self, attn, query, key, D, per_head):
@@ -78,8 +89,9 @@ class _ProcessorBase:
             out.append((t, spec))
         return out[0][0], out[1][0], out[0][1], out[1][1]
 
-    def _attend(self, query, key, value, n_text, use_rope, q_norm=None, k_norm=None):
-        """query/key/value: [B, N, H*D] projections; returns [B, N, H*D]."""
+    def _attend(self, query, key, value, n_text, rotary, q_norm=None, k_norm=None):
+        """query/key/value: [B, N, H*D] projections; rotary: the embedding passed to the processor (None =
+        no rotation).  Returns [B, N, H*D]."""
         B, N, inner = query.shape
         H = self._heads
         D = inner // H
@@ -89,8 +101,9 @@ class _ProcessorBase:
         start.record()
         out = paro_attention(q, k, v, pplan, splan, i_block=self.i_block, i_timestep=self.i_timestep,
                              grid_fhw=self.grid_fhw, n_text=n_text,
-                             rope=self._rope(D, query.device) if use_rope else None,
-                             tensor_layout="NHD", smooth_k=self.smooth_k, q_norm=q_norm, k_norm=k_norm)
+                             rope=self._rope(D, query.device, rotary) if rotary is not None else None,
+                             tensor_layout="NHD", smooth_k=self.smooth_k, q_norm=q_norm, k_norm=k_norm,
+                             empty_head_mode=self.empty_head_mode)
         if isinstance(splan, PlanStore):     # stream the next layer's lists in while this layer computes
             splan.prefetch(self.i_timestep, self.i_block + 1)
         end.record()
@@ -103,6 +116,7 @@ class _ProcessorBase:
         resolved here instead of synchronising the device after every layer (cogvideox.py:224)."""
         if self._pending:
             torch.cuda.synchronize()
+            check_status()            # a launch that gave up a wait must not pass as a timing
             for s, e in self._pending:
                 self.time_accum["total"] += s.elapsed_time(e)
             self._pending.clear()
@@ -111,8 +125,9 @@ class _ProcessorBase:
 
 class PARO_CogVideoXAttnProcessor2_0(_ProcessorBase):
     """CogVideoX joint text+video self-attention (reference: cogvideox.py:112-250).  When
-    `image_rotary_emb` is given, the 3-D rotary embedding is applied inside the fused
-    RoPE+permute pass from tables built for `grid_fhw` (the passed tensor itself is not read)."""
+    `image_rotary_emb` = (cos, sin) is given, the rotation is applied inside the fused RoPE+permute pass
+    with the angles of that embedding (reduced once to per-axis tables; an embedding that is not a 3-D
+    table over `grid_fhw` raises)."""
     default_grid = (13, 30, 45)
     rope_family = "cogvideox"
 
@@ -126,7 +141,7 @@ class PARO_CogVideoXAttnProcessor2_0(_ProcessorBase):
         B, N, inner = key.shape
         D = inner // attn.heads
         query, key, q_norm, k_norm = self._norms(attn, query, key, D, per_head=True)
-        hidden_states = self._attend(query, key, value, text_seq_length, image_rotary_emb is not None, q_norm, k_norm)
+        hidden_states = self._attend(query, key, value, text_seq_length, image_rotary_emb, q_norm, k_norm)
         hidden_states = attn.to_out[0](hidden_states)
         hidden_states = attn.to_out[1](hidden_states)
         encoder_hidden_states, hidden_states = hidden_states.split(
@@ -150,7 +165,7 @@ class PARO_WanAttnProcessor2_0(_ProcessorBase):
         query, key, value = attn.to_q(hidden_states), attn.to_k(hidden_states), attn.to_v(hidden_states)
         D = query.shape[-1] // attn.heads
         query, key, q_norm, k_norm = self._norms(attn, query, key, D, per_head=False)
-        hidden_states = self._attend(query, key, value, 0, rotary_emb is not None, q_norm, k_norm)
+        hidden_states = self._attend(query, key, value, 0, rotary_emb, q_norm, k_norm)
         hidden_states = attn.to_out[0](hidden_states)
         hidden_states = attn.to_out[1](hidden_states)
         return hidden_states
@@ -173,6 +188,8 @@ class TimestepCallback:
         pipeline.transformer.i_timestep = self.sparse_mask_timestep
         for block in pipeline.transformer.transformer_blocks:
             block.attn1.processor.i_timestep = self.sparse_mask_timestep
+        if torch.cuda.is_available():
+            check_status()     # once per denoising step: stop the run if an attention launch gave up a wait
         return callback_kwargs
 
     __call__ = on_step_end

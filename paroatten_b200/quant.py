@@ -22,7 +22,8 @@ def _hnd(x: torch.Tensor, tensor_layout: str) -> torch.Tensor:
 
 def _stats_scratch(B, H, N, D, device) -> torch.Tensor:
     need = _lib.lib().paro_channel_stats_scratch_bytes(B, H, N, D)
-    key = (device.index if device.index is not None else torch.cuda.current_device())
+    # one buffer per device AND stream: two streams reducing at once must not share partial sums
+    key = (device.index if device.index is not None else torch.cuda.current_device(), _lib.stream_ptr())
     buf = _scratch.get(key)
     if buf is None or buf.numel() < need:
         buf = torch.empty(need, dtype=torch.uint8, device=device)
@@ -65,30 +66,69 @@ def _quant_int8(x, tensor_layout, group, km=None, fold=0.0):
     return out, scale
 
 
+def _quant_int8_blocks_of(x, tensor_layout, block, km=None, fold=0.0):
+    """Per-`block`-token INT8 for block sizes the CUDA pass does not take (the reference's default
+    BLKQ = 128), with torch elementwise ops and the same arithmetic (fused.cu:95-197): a compatibility
+    route for callers of the quantisers alone -- the attention path of this library always uses 64-token
+    blocks, the sparse plan's granularity.  Returns (int8 like x, fp32 scale [B,H,ceil(N/block)])."""
+    _lib.require_cuda(x, km)
+    xv = _hnd(x, tensor_layout)
+    B, H, N, D = xv.shape
+    xf = xv.float()
+    if km is not None:
+        xf = xf - km.reshape(B, H, 1, D).to(x.dtype).float()
+    if fold:
+        xf = xf * torch.tensor(fold, dtype=torch.float32, device=x.device)
+    nblk = (N + block - 1) // block
+    pad = nblk * block - N
+    if pad:
+        xf = torch.nn.functional.pad(xf, (0, 0, 0, pad))
+    g = xf.reshape(B, H, nblk, block * D)
+    amax = g.abs().amax(dim=-1).clamp_min(1e-7)
+    scale = amax / 127.0
+    inv = torch.div(torch.full_like(amax, 127.0), amax)     # one IEEE division (scalar / tensor would be reciprocal * scalar)
+    q8 = torch.round(g * inv.unsqueeze(-1)).clamp_(-128, 127).to(torch.int8)
+    q8 = q8.reshape(B, H, nblk * block, D)[:, :, :N].contiguous()
+    return (q8.transpose(1, 2) if tensor_layout == "NHD" else q8), scale.contiguous()
+
+
 def per_block_int8(q, k, km: Optional[torch.Tensor] = None, BLKQ: int = 128, BLKK: int = 64,
                    sm_scale: Optional[float] = None, tensor_layout: str = "HND"):
-    """Reference signature paroattention/quant.py:22-103: Q per block with sm_scale*log2(e) folded
-    in, K per block (optionally mean-smoothed).  Only 64-token blocks are supported (the sparse
-    plan's granularity); the reference default BLKQ=128 is rejected."""
-    if BLKQ != 64 or BLKK != 64:
-        raise ValueError("paroatten_b200 quantises in 64-token blocks: pass BLKQ=64, BLKK=64")
+    """Reference signature and defaults of paroattention/quant.py:22-103: Q per block of BLKQ tokens with
+    sm_scale*log2(e) folded in, K per block of BLKK tokens (optionally mean-smoothed).  64-token blocks
+    run in the CUDA quantiser; 128-token blocks (the reference's default BLKQ) take the torch route of
+    _quant_int8_blocks_of.  The attention entry points of this library quantise with 64-token blocks."""
+    if BLKQ not in (64, 128) or BLKK not in (64, 128):
+        raise ValueError("per_block_int8: BLKQ and BLKK must be 64 or 128")
     D = q.shape[-1]
     if sm_scale is None:
         sm_scale = D ** -0.5
-    q8, qs = _quant_int8(q, tensor_layout, 64, fold=sm_scale * 1.44269504)
-    k8, ks = _quant_int8(k, tensor_layout, 64, km=km)
+    fold = sm_scale * 1.44269504
+    q8, qs = (_quant_int8(q, tensor_layout, 64, fold=fold) if BLKQ == 64
+              else _quant_int8_blocks_of(q, tensor_layout, BLKQ, fold=fold))
+    k8, ks = (_quant_int8(k, tensor_layout, 64, km=km) if BLKK == 64
+              else _quant_int8_blocks_of(k, tensor_layout, BLKK, km=km))
     return q8, qs, k8, ks
 
 
 def per_warp_int8(q, k, km: Optional[torch.Tensor] = None, BLKQ: int = 128, WARPQ: int = 32, BLKK: int = 64,
                   tensor_layout: str = "HND"):
-    """Reference signature paroattention/quant.py:105-180: Q per 32-row group (two scales per
-    64-token block), K per 64-token block (optionally mean-smoothed).  The processors call it
-    with BLKQ=64, WARPQ=32, BLKK=64 (cogvideox.py:186); that is the supported setting."""
-    if BLKQ != 64 or WARPQ != 32 or BLKK != 64:
-        raise ValueError("paroatten_b200 supports BLKQ=64, WARPQ=32, BLKK=64")
+    """Reference signature and defaults of paroattention/quant.py:105-180: Q per WARPQ = 32 rows, K per
+    block of BLKK tokens (optionally mean-smoothed).  BLKQ only sets how far the Q scale array is padded:
+    (ceil(N/BLKQ) * BLKQ/32) entries, the trailing ones belonging to groups past the end of the sequence
+    (quant.py:169).  The processors call it with BLKQ=64, WARPQ=32, BLKK=64 (cogvideox.py:186); that is also
+    the layout the attention kernel reads.  WARPQ = 16 is not supported."""
+    if BLKQ not in (64, 128) or WARPQ != 32 or BLKK not in (64, 128):
+        raise ValueError("per_warp_int8: BLKQ and BLKK must be 64 or 128, WARPQ must be 32")
     q8, qs = _quant_int8(q, tensor_layout, 32)
-    k8, ks = _quant_int8(k, tensor_layout, 64, km=km)
+    if BLKQ == 128:
+        n = q.shape[2] if tensor_layout == "HND" else q.shape[1]
+        want = (n + 127) // 128 * 4
+        if want != qs.shape[-1]:       # two more 32-row groups of padding: all zeros, amax floor 1e-7
+            qs = torch.cat([qs, torch.full((*qs.shape[:-1], want - qs.shape[-1]), 1e-7 / 127.0,
+                                           dtype=qs.dtype, device=qs.device)], dim=-1)
+    k8, ks = (_quant_int8(k, tensor_layout, 64, km=km) if BLKK == 64
+              else _quant_int8_blocks_of(k, tensor_layout, BLKK, km=km))
     return q8, qs, k8, ks
 
 

@@ -105,6 +105,49 @@ def rope_tables(grid, head_dim: int, family: str, theta: float = 10000.0, device
     return RopeTables(mode, cos.to(device).contiguous(), sin.to(device).contiguous(), pairs[0], pairs[1])
 
 
+def tables_from_embedding(emb, grid, head_dim: int, family: str, device=None) -> RopeTables:
+    """Per-axis tables taken from the rotary embedding a pipeline hands to the processor, so that the
+    processor rotates by exactly the angles it was given (another theta, a cropped or rescaled grid):
+      "cogvideox": emb = (cos, sin), each [F*H*W, D] fp32 with every angle repeated for its channel pair
+                   (diffusers' real layout; paroattention/cogvideox.py:167-172 passes it on unchanged);
+      "wan":       emb = complex128 [1, 1, F*H*W, D/2] (WanRotaryPosEmbed, paroattention/wan.py:482-522).
+    A 3-D table depends on one coordinate per channel pair, so the rows of tokens (f,0,0), (0,y,0), (0,0,x)
+    hold everything; the result is checked by rebuilding the full table from the per-axis rows and
+    comparing it with `emb` exactly -- ValueError if the embedding is not of that separable form."""
+    F, Hh, W = (int(g) for g in grid)
+    n_img, half = F * Hh * W, head_dim // 2
+    if family == "cogvideox":
+        cos_full, sin_full = (t.reshape(n_img, head_dim)[:, 0::2].to(torch.float32) for t in emb)
+        mode = _lib.ROPE_REAL_F32
+    elif family == "wan":
+        e = emb.reshape(n_img, half)
+        cos_full, sin_full = e.real.to(torch.float64), e.imag.to(torch.float64)
+        mode = _lib.ROPE_COMPLEX_F64
+    else:
+        raise ValueError(f"unknown rope family {family!r}")
+    device = cos_full.device if device is None else torch.device(device)
+    cos_full, sin_full = cos_full.to(device), sin_full.to(device)
+    pf, ph, pw = axis_pairs(head_dim, family)
+    rows = (torch.arange(F, device=device) * (Hh * W), torch.arange(Hh, device=device) * W, torch.arange(W, device=device))
+    cols = ((0, pf), (pf, pf + ph), (pf + ph, half))
+    cos = torch.ones(F + Hh + W, half, dtype=cos_full.dtype, device=device)
+    sin = torch.zeros(F + Hh + W, half, dtype=cos_full.dtype, device=device)
+    r0 = 0
+    for idx, (c0, c1) in zip(rows, cols):
+        cos[r0:r0 + idx.numel(), c0:c1] = cos_full[idx, c0:c1]
+        sin[r0:r0 + idx.numel(), c0:c1] = sin_full[idx, c0:c1]
+        r0 += idx.numel()
+    # rebuild and compare
+    n = torch.arange(n_img, device=device)
+    f, y, x = n // (Hh * W), (n // W) % Hh, n % W
+    for full, tab in ((cos_full, cos), (sin_full, sin)):
+        back = torch.cat([tab[f, 0:pf], tab[F + y, pf:pf + ph], tab[F + Hh + x, pf + ph:half]], dim=1)
+        if not torch.equal(back, full):
+            raise ValueError(f"the rotary embedding is not a per-axis 3-D table over the grid {tuple(grid)} with "
+                             f"{pf}/{ph}/{pw} channel pairs per axis; set processor.grid_fhw to the latent grid")
+    return RopeTables(mode, cos.contiguous(), sin.contiguous(), pf, ph)
+
+
 def rope_permute(x: torch.Tensor, order_ids: Optional[torch.Tensor], grid, n_text: int = 0,
                  rope: Optional[RopeTables] = None, inverse: bool = False,
                  tensor_layout: str = "HND", norm: Optional[QKNorm] = None) -> torch.Tensor:

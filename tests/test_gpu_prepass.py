@@ -159,7 +159,7 @@ def test_argument_errors():
     with pytest.raises(ValueError, match="head_dim"):
         pb.per_warp_int8(x, x, BLKQ=64, WARPQ=32, BLKK=64)
     with pytest.raises(ValueError):
-        pb.per_warp_int8(x, x)  # reference default BLKQ=128 is not supported
+        pb.per_warp_int8(x[..., :64].contiguous(), x[..., :64].contiguous(), WARPQ=16)
     y = torch.zeros(1, 1, 64, 64, dtype=torch.float32, device=DEV)
     with pytest.raises(ValueError, match="dtype"):
         pb.per_channel_fp8(y)
@@ -258,3 +258,23 @@ def test_qk_norm_argument_errors():
         pb.rope_permute(x, None, (1, 8, 8), norm=pb.QKNorm("batch", torch.ones(64, device=DEV)))
     with pytest.raises(ValueError):
         pb.rope_permute(x, None, (1, 8, 8), inverse=True, norm=pb.QKNorm("layer", torch.ones(64, device=DEV)))
+
+
+@pytest.mark.parametrize("N,D,dtype", [(300, 64, torch.float16), (1000, 128, torch.bfloat16)])
+def test_reference_default_block_sizes(N, D, dtype):
+    """per_warp_int8 / per_block_int8 called with the reference's defaults (BLKQ=128,
+    paroattention/quant.py:22-30,105-112): same values as the oracle's per-128 quantiser; per-warp Q
+    only differs from the BLKQ=64 call in the padding of its scale array."""
+    B, H = 2, 3
+    q, k = rand((B, H, N, D), dtype, 61), rand((B, H, N, D), dtype, 62, offset=0.5)
+    q8, qs, k8, ks = pb.per_warp_int8(q.to(DEV), k.to(DEV))                      # BLKQ=128, WARPQ=32, BLKK=64
+    w8, ws = po.quant_int8(q, 32)
+    assert torch.equal(q8.cpu(), w8) and qs.shape[-1] == (N + 127) // 128 * 4
+    assert torch.equal(qs.cpu()[..., :ws.shape[-1]], ws)
+    assert torch.equal(k8.cpu(), po.quant_int8(k, 64)[0])
+    sm = D ** -0.5
+    q8b, qsb, k8b, ksb = pb.per_block_int8(q.to(DEV), k.to(DEV), sm_scale=sm)     # BLKQ=128, BLKK=64
+    w8b, wsb = po.quant_int8(q, 128, fold_scale=sm * 1.44269504)
+    assert qsb.shape == wsb.shape == (B, H, (N + 127) // 128)
+    assert torch.equal(q8b.cpu(), w8b) and torch.equal(qsb.cpu(), wsb)
+    assert torch.equal(k8b.cpu(), po.quant_int8(k, 64)[0]) and torch.equal(ksb.cpu(), po.quant_int8(k, 64)[1])
