@@ -89,7 +89,9 @@ int paro_channel_mean(const void* x, int dtype, int B, int H, int N, int D,
  *   - B*H*ceil(N/512)*D*16 bytes must fit in 16 MiB, otherwise PARO_ECAP (nothing is launched);
  *   - the call allocates nothing (no cudaMalloc/cudaFree, no allocating library routine);
  *   - the first call on each device looks up the array's device address (cudaGetSymbolAddress),
- *     so make that first call before starting any stream capture;
+ *     so make that first call before starting any stream capture -- and during warm-up: with
+ *     CUDA's lazy module loading it is also the moment the driver places the 16 MiB array in that
+ *     GPU's memory, so on a GPU with no room left this first call can fail with PARO_ECUDA;
  *   - all calls on a device share the one array: calls that may overlap on the GPU (different
  *     streams without ordering) race and must be serialised by the caller.  The array keeps the
  *     previous call's contents; every value a call reads is written by that call first. */

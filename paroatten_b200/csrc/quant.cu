@@ -501,7 +501,7 @@ extern "C" int paro_quant_v_fp8(const void* v, int dtype, int B, int H, int N, i
 // loads the library sets aside its 16 MiB until the process exits.
 namespace {
 
-constexpr size_t NOALLOC_SCRATCH_BYTES = 16u << 20;   // 16 MiB: enough for B*H*ceil(N/512)*D <= 1,040,000
+constexpr size_t NOALLOC_SCRATCH_BYTES = 16u << 20;   // 16 MiB = 1,048,576 partials of 16 bytes: B*H*ceil(N/512)*D may not exceed that
 static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_SCRATCH_BYTES];
 
 constexpr int NOALLOC_MAX_DEVICES = 64;

@@ -85,7 +85,7 @@ def _quant_int8_blocks_of(x, tensor_layout, block, km=None, fold=0.0):
         xf = torch.nn.functional.pad(xf, (0, 0, 0, pad))
     g = xf.reshape(B, H, nblk, block * D)
     amax = g.abs().amax(dim=-1).clamp_min(1e-7)
-    scale = amax / 127.0
+    scale = torch.div(amax, torch.full_like(amax, 127.0))    # (a tensor / scalar division multiplies by the reciprocal)
     inv = torch.div(torch.full_like(amax, 127.0), amax)     # one IEEE division (scalar / tensor would be reciprocal * scalar)
     q8 = torch.round(g * inv.unsqueeze(-1)).clamp_(-128, 127).to(torch.int8)
     q8 = q8.reshape(B, H, nblk * block, D)[:, :, :N].contiguous()

@@ -58,3 +58,37 @@ def test_noalloc_strided_input_and_limit():
                                      _lib.stream_ptr())
     assert rc == _lib.PARO_ECAP and b"built-in scratch" in L.paro_last_error()
     assert L.paro_launch_count() == before
+
+
+def test_noalloc_capacity_edge_and_no_allocation():
+    """At the limit of the built-in array (1,048,576 partial sums of 16 bytes) the call runs, one chunk of
+    tokens more is refused; and a call takes no device memory: what the driver reports as free and what
+    torch's allocator holds are the same before and after (after a first call, which is when the driver
+    places the library's array).  Batch and head strides of 0 make a large problem out of one small tensor."""
+    L = _lib.lib()
+    D, B, H = 128, 64, 128                       # B*H*D = 1,048,576: exactly one 512-token chunk fits
+    row = (torch.arange(D, dtype=torch.float32, device="cuda") / 8 - 3).to(torch.float16).reshape(1, D)
+    rows = row.expand(513, D).contiguous()       # 513 equal tokens, shared by every (batch entry, head)
+    out32 = torch.empty(B, H, D, dtype=torch.float32, device="cuda")
+
+    def call(n_tokens):
+        return L.paro_channel_mean_noalloc(rows.data_ptr(), _lib.F16, B, H, n_tokens, D, 0, 0, D, None, out32.data_ptr(),
+                                           _lib.stream_ptr())
+    assert call(512) == 0, L.paro_last_error().decode()
+    torch.cuda.synchronize()
+    assert torch.equal(out32, row.float().reshape(1, 1, D).expand(B, H, D))     # the mean of equal rows is the row
+    before = L.paro_launch_count()
+    assert call(513) == _lib.PARO_ECAP and b"built-in scratch" in L.paro_last_error()
+    assert L.paro_launch_count() == before
+    # no device memory is taken by a call
+    x = torch.randn(2, 4, 3000, 64, device="cuda").to(torch.bfloat16)
+    out = torch.empty(2, 4, 64, dtype=torch.bfloat16, device="cuda")
+    args = (x.data_ptr(), _lib.BF16, 2, 4, 3000, 64, x.stride(0), x.stride(1), x.stride(2), out.data_ptr(), None,
+            _lib.stream_ptr())
+    assert L.paro_channel_mean_noalloc(*args) == 0
+    torch.cuda.synchronize()
+    free0, held0 = torch.cuda.mem_get_info()[0], torch.cuda.memory_allocated()
+    for _ in range(3):
+        assert L.paro_channel_mean_noalloc(*args) == 0
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free0 and torch.cuda.memory_allocated() == held0
