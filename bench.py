@@ -34,7 +34,7 @@ DTYPE = "int8 QK^T (s32 acc), bf16 PV (f32 acc), fp32 softmax"
 # DRAM bytes of one attention launch per (batch entry, head, token) at D = 128, from one ncu capture of a
 # B=2 H=12 N=32760 launch (read + written = int8 Q, K + 16-bit V + 16-bit O, i.e. the compulsory bytes);
 # the traffic of other D = 128 shapes is this figure times B*H*N, to which those bytes are proportional.
-ATTN_DRAM_BYTES_PER_BHN_D128 = 589.1e6 / (2 * 12 * 32760)
+ATTN_DRAM_BYTES_PER_BHN_D128 = 588.5e6 / (2 * 12 * 32760)
 
 
 def config_of(name, wl, world):

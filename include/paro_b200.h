@@ -61,6 +61,8 @@ int paro_build_perm_index(const int32_t* order_ids, int H, int F, int Hh, int W,
  * PARO_ROPE_REAL_F32 (pairs (2i,2i+1): o0=x0*c-x1*s, o1=x1*c+x0*s, as diffusers'
  * apply_rotary_emb at cogvideox.py:167-172), fp64 for PARO_ROPE_COMPLEX_F64 (wan.py:161-164).
  * pairs_f/pairs_h: how many leading channel pairs follow the f / h coordinate (rest: w).
+ * sin_tab == NULL (all entry points that take the two tables): cos_tab is then ONE table
+ * [F+Hh+W, D/2, 2] with cos and sin of a pair side by side, fetched by a single load.
  * Replaces csrc/rope/rope.cu:14-48 (rope_permutation) and permute_qk / permute_attn_out
  * (cogvideox.py:22-110). */
 int paro_rope_permute(const void* in, void* out, int dtype, int B, int H, int N, int D,

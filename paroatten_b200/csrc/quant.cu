@@ -569,7 +569,7 @@ int make_gather(Gather* g, const char* who, int N, int D, int n_text, int F, int
   PARO_REQUIRE(rope_mode >= PARO_ROPE_NONE && rope_mode <= PARO_ROPE_COMPLEX_F64, PARO_EINVAL,
                "%s: unknown rope_mode %d", who, rope_mode);
   if (rope_mode != PARO_ROPE_NONE) {
-    PARO_REQUIRE(cos_tab && sin_tab, PARO_EINVAL, "%s: rope tables missing", who);
+    PARO_REQUIRE(cos_tab, PARO_EINVAL, "%s: rope tables missing", who);   // sin_tab NULL = interleaved (cos, sin) table
     PARO_REQUIRE(pairs_f >= 0 && pairs_h >= 0 && pairs_f + pairs_h <= D / 2, PARO_ESHAPE,
                  "%s: pairs_f + pairs_h exceeds D/2", who);
   }

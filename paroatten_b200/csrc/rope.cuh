@@ -6,8 +6,8 @@ namespace paro {
 
 struct RopeArgs {
   int mode;            // PARO_ROPE_*
-  const void* cos_tab; // [F+Hh+W, D/2]
-  const void* sin_tab;
+  const void* cos_tab; // [F+Hh+W, D/2]; or, when sin_tab is NULL, [F+Hh+W, D/2, 2] holding (cos, sin) side by side
+  const void* sin_tab; // [F+Hh+W, D/2] or NULL (one 8- or 16-byte load then fetches both values of a pair)
   int pairs_f, pairs_h;
 };
 
@@ -26,8 +26,14 @@ __device__ __forceinline__ void rotate8(Pack8<T>& x, int c8, int D, int f, int y
     const int row = pair < r.pairs_f ? f : (pair < r.pairs_f + r.pairs_h ? F + y : F + Hh + xw);
     const size_t t = (size_t)row * half + pair;
     if constexpr (MODE == PARO_ROPE_REAL_F32) {
-      const float c = static_cast<const float*>(r.cos_tab)[t];
-      const float s = static_cast<const float*>(r.sin_tab)[t];
+      float c, s;
+      if (r.sin_tab == nullptr) {
+        const float2 cs = static_cast<const float2*>(r.cos_tab)[t];
+        c = cs.x; s = cs.y;
+      } else {
+        c = static_cast<const float*>(r.cos_tab)[t];
+        s = static_cast<const float*>(r.sin_tab)[t];
+      }
       const float x0 = F16Traits<T>::to_float(x.e[2 * p]);
       const float x1 = F16Traits<T>::to_float(x.e[2 * p + 1]);
       const float o0 = __fadd_rn(__fmul_rn(x0, c), __fmul_rn(-x1, s));
@@ -35,8 +41,14 @@ __device__ __forceinline__ void rotate8(Pack8<T>& x, int c8, int D, int f, int y
       x.e[2 * p] = F16Traits<T>::from_float(o0);
       x.e[2 * p + 1] = F16Traits<T>::from_float(o1);
     } else {
-      const double c = static_cast<const double*>(r.cos_tab)[t];
-      const double s = static_cast<const double*>(r.sin_tab)[t];
+      double c, s;
+      if (r.sin_tab == nullptr) {
+        const double2 cs = static_cast<const double2*>(r.cos_tab)[t];
+        c = cs.x; s = cs.y;
+      } else {
+        c = static_cast<const double*>(r.cos_tab)[t];
+        s = static_cast<const double*>(r.sin_tab)[t];
+      }
       const double x0 = (double)F16Traits<T>::to_float(x.e[2 * p]);
       const double x1 = (double)F16Traits<T>::to_float(x.e[2 * p + 1]);
       const double re = __dsub_rn(__dmul_rn(x0, c), __dmul_rn(x1, s));

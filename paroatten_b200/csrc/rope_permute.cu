@@ -147,7 +147,7 @@ extern "C" int paro_rope_permute(const void* in, void* out, int dtype, int B, in
   PARO_REQUIRE(!(inverse && rope_mode != PARO_ROPE_NONE), PARO_EINVAL,
                "paro_rope_permute: the inverse permutation does not rotate");
   if (rope_mode != PARO_ROPE_NONE) {
-    PARO_REQUIRE(cos_tab && sin_tab, PARO_EINVAL, "paro_rope_permute: rope tables missing");
+    PARO_REQUIRE(cos_tab, PARO_EINVAL, "paro_rope_permute: rope tables missing");   // sin_tab NULL = interleaved (cos, sin) table
     PARO_REQUIRE(pairs_f >= 0 && pairs_h >= 0 && pairs_f + pairs_h <= D / 2, PARO_ESHAPE,
                  "paro_rope_permute: pairs_f + pairs_h exceeds D/2");
   }
@@ -174,7 +174,7 @@ extern "C" int paro_rope_permute_norm(const void* in, void* out, int dtype, int 
   PARO_REQUIRE(rope_mode >= PARO_ROPE_NONE && rope_mode <= PARO_ROPE_COMPLEX_F64, PARO_EINVAL,
                "paro_rope_permute_norm: unknown rope_mode %d", rope_mode);
   if (rope_mode != PARO_ROPE_NONE) {
-    PARO_REQUIRE(cos_tab && sin_tab, PARO_EINVAL, "paro_rope_permute_norm: rope tables missing");
+    PARO_REQUIRE(cos_tab, PARO_EINVAL, "paro_rope_permute_norm: rope tables missing");
     PARO_REQUIRE(pairs_f >= 0 && pairs_h >= 0 && pairs_f + pairs_h <= D / 2, PARO_ESHAPE,
                  "paro_rope_permute_norm: pairs_f + pairs_h exceeds D/2");
   }

@@ -11,14 +11,16 @@ import torch
 from . import _lib
 
 
-@dataclass
 class RopeTables:
-    """Per-axis angle tables [F+H+W, D/2]: row = axis base + coordinate, column = channel pair."""
-    mode: int            # _lib.ROPE_REAL_F32 or _lib.ROPE_COMPLEX_F64
-    cos: torch.Tensor
-    sin: torch.Tensor
-    pairs_f: int
-    pairs_h: int
+    """Per-axis angle tables: row = axis base + coordinate, column = channel pair.  Built from cos and sin
+    tables [F+H+W, D/2] and handed to the kernels as ONE table [F+H+W, D/2, 2] with cos and sin of a pair side
+    by side (a single load fetches both): `.cos` is that table, `.sin` is None."""
+
+    def __init__(self, mode: int, cos: torch.Tensor, sin: torch.Tensor, pairs_f: int, pairs_h: int):
+        self.mode = mode            # _lib.ROPE_REAL_F32 or _lib.ROPE_COMPLEX_F64
+        self.cos = torch.stack([cos, sin], dim=-1).contiguous()
+        self.sin = None
+        self.pairs_f, self.pairs_h = pairs_f, pairs_h
 
 
 @dataclass
