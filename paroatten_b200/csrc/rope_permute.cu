@@ -8,7 +8,8 @@
 
 namespace paro {
 
-// Block = 256 threads; a thread owns one 16-byte slice of a row and walks ROWS_PER_THREAD rows.
+// Block = 256 threads; a thread owns one 16-byte slice of PASSES consecutive rows (consecutive rows share
+// the slow grid coordinates, so most of their rotation angles are reused from registers).
 // blockIdx.x: group of rows, blockIdx.y: b*H + h.
 template <typename T, int D, int MODE, int NM>
 __global__ void __launch_bounds__(256)
@@ -20,7 +21,7 @@ rope_permute_kernel(const T* __restrict__ in, T* __restrict__ out, int H, int N,
   constexpr int PASSES = 4;
   const int bh = blockIdx.y, b = bh / H, h = bh % H;
   const int c8 = (threadIdx.x % TPR) * 8;
-  const int r0 = blockIdx.x * (ROWS * PASSES) + threadIdx.x / TPR;
+  const int r0 = blockIdx.x * (ROWS * PASSES) + (threadIdx.x / TPR) * PASSES;
   const PermDecoder dec(order_ids ? order_ids[h] : 0, F, Hh, W);
   const T* src_base = in + b * sb + h * sh;
   T* dst_base = out + (size_t)bh * N * D;
@@ -29,7 +30,7 @@ rope_permute_kernel(const T* __restrict__ in, T* __restrict__ out, int H, int N,
   int dst_row[PASSES], src_row[PASSES], fy[PASSES], yy[PASSES], xx[PASSES];
 #pragma unroll
   for (int i = 0; i < PASSES; ++i) {
-    const int row = r0 + i * ROWS;
+    const int row = r0 + i;
     dst_row[i] = -1;
     src_row[i] = 0;
     val[i].v = make_uint4(0, 0, 0, 0);
@@ -55,13 +56,14 @@ rope_permute_kernel(const T* __restrict__ in, T* __restrict__ out, int H, int N,
     src_row[i] = src;
     val[i].v = *reinterpret_cast<const uint4*>(src_base + (size_t)src * sn + c8);
   }
+  [[maybe_unused]] RotCache<MODE == PARO_ROPE_REAL_F32 ? PARO_ROPE_REAL_F32 : PARO_ROPE_COMPLEX_F64> rot;
 #pragma unroll
   for (int i = 0; i < PASSES; ++i) {
     // every lane takes part in the normalisation's shuffles, also those whose row is past the end
     if constexpr (NM != PARO_NORM_NONE) normalize8<T, NM, TPR>(val[i], c8, D, b, h, N, src_row[i], norm);
     if (dst_row[i] < 0) continue;
     if constexpr (MODE != PARO_ROPE_NONE) {
-      if (fy[i] >= 0) rotate8<T, MODE>(val[i], c8, D, fy[i], yy[i], xx[i], F, Hh, rope);
+      if (fy[i] >= 0) rotate8<T, MODE>(val[i], c8, D, fy[i], yy[i], xx[i], F, Hh, rope, rot);
     }
     *reinterpret_cast<uint4*>(dst_base + (size_t)dst_row[i] * D + c8) = val[i].v;
   }
