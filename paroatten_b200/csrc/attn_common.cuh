@@ -14,7 +14,7 @@ constexpr int TMEM_COLS = 256;
 constexpr long long WAIT_LIMIT = 400000000;  // SM cycles (~0.2 s) before a wait gives up
 constexpr float SCORE_BIAS = 12582912.0f;    // 1.5 * 2^23, bit pattern 0x4B400000
 
-// Words of the redo work space handed to paro_sparse_attn: [0] number of work items the fast walk
+// Words of the redo work space handed to paro_sparse_attn: [0] number of work items the fixed-reference walk
 // gave back, [1..] the items (block indices of the fast launch).
 constexpr int REDO_HEADER = 1;
 

@@ -77,7 +77,7 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
                          const AttnParams p) {
   using Cfg = AttnCfg<D>;
   constexpr int KST = Cfg::K_STAGES, VST = Cfg::V_STAGES;
-  // second launch of a call: only the work items the fast walk gave back
+  // second launch of a call: only the work items the fixed-reference walk gave back
   if (p.from_list && (int)blockIdx.x >= *reinterpret_cast<volatile int32_t*>(p.redo)) return;
 
   extern __shared__ uint8_t smem_raw[];
@@ -708,7 +708,7 @@ extern "C" int paro_sparse_attn(const int8_t* q8, const int8_t* k8, const uint16
   PARO_REQUIRE(sm_scale > 0.f, PARO_EINVAL, "paro_sparse_attn: sm_scale must be positive");
   PARO_REQUIRE(mode == PARO_ATTN_FAST || mode == PARO_ATTN_EXACT, PARO_EINVAL, "paro_sparse_attn: unknown mode %d", mode);
   PARO_REQUIRE(mode == PARO_ATTN_EXACT || (redo && redo_bytes >= paro_sparse_attn_redo_bytes(B, H, N)), PARO_ECAP,
-               "paro_sparse_attn: the fast walk needs a redo work space of paro_sparse_attn_redo_bytes() bytes");
+               "paro_sparse_attn: PARO_ATTN_FAST needs a redo work space of paro_sparse_attn_redo_bytes() bytes");
   AttnParams p;
   p.q8 = q8; p.q_scale = q_scale; p.k_scale = k_scale; p.v_scale = v_scale; p.vm = vm;
   p.pair_ptr = pair_ptr; p.sched = sched; p.sched_cnt = sched_cnt; p.inv_idx = inv_idx;
