@@ -48,14 +48,11 @@ struct GatherCtx {
     const int src = g.n_text + dec.source(tok - g.n_text, f, y, x);
     return src;
   }
-  // angles kept from row to row by the caller (one per thread), see rope.cuh
-  using Cache = RotCache<GM == GM_ROPE_F32 ? PARO_ROPE_REAL_F32 : PARO_ROPE_COMPLEX_F64>;
-  template <typename T>
-  __device__ __forceinline__ void rotate(Pack8<T>& v, int c8, int D, int f, int y, int x, Cache& cache) const {
+  template <typename T> __device__ __forceinline__ void rotate(Pack8<T>& v, int c8, int D, int f, int y, int x) const {
     if constexpr (GM == GM_ROPE_F32) {
-      if (f >= 0) rotate8<T, PARO_ROPE_REAL_F32>(v, c8, D, f, y, x, g.F, g.Hh, g.rope, cache);
+      if (f >= 0) rotate8<T, PARO_ROPE_REAL_F32>(v, c8, D, f, y, x, g.F, g.Hh, g.rope);
     } else if constexpr (GM == GM_ROPE_F64) {
-      if (f >= 0) rotate8<T, PARO_ROPE_COMPLEX_F64>(v, c8, D, f, y, x, g.F, g.Hh, g.rope, cache);
+      if (f >= 0) rotate8<T, PARO_ROPE_COMPLEX_F64>(v, c8, D, f, y, x, g.F, g.Hh, g.rope);
     }
   }
 };
@@ -97,7 +94,6 @@ channel_stats_kernel(const T* __restrict__ x, int H, int N, int64_t sb, int64_t 
   const GatherCtx<GM> gc(gather, h);
   double sum[8];
   float mx[8], mn[8];
-  [[maybe_unused]] typename GatherCtx<GM>::Cache rot;
 #pragma unroll
   for (int j = 0; j < 8; ++j) { sum[j] = 0.0; mx[j] = -INFINITY; mn[j] = INFINITY; }
   // four rows are in flight per thread; they are accumulated in the order of a plain loop
@@ -113,7 +109,7 @@ channel_stats_kernel(const T* __restrict__ x, int H, int N, int64_t sb, int64_t 
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
       if (t + u * ROWS >= t1) break;
-      gc.rotate(v[u], c8, D, gf[u], gy[u], gx[u], rot);
+      gc.rotate(v[u], c8, D, gf[u], gy[u], gx[u]);
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         const float f = F16Traits<T>::to_float(v[u].e[j]);
@@ -208,7 +204,6 @@ quant_int8_kernel(const T* __restrict__ x, const T* __restrict__ km, int8_t* __r
   // Each of the warp's 16 tokens is decoded once (source token and grid position) by lane t and
   // lane t+16, and handed to the threads that load it.
   int d_src = 0, d_f = -1, d_y = -1, d_x = -1;
-  [[maybe_unused]] typename GatherCtx<GM>::Cache rot;
   if constexpr (GM != GM_PLAIN) {
     const int t = blockIdx.x * 64 + warp * 16 + (lane & 15);
     if (t < N) d_src = gc.source(t, d_f, d_y, d_x);
@@ -234,7 +229,7 @@ quant_int8_kernel(const T* __restrict__ x, const T* __restrict__ km, int8_t* __r
       const int gf = __shfl_sync(0xffffffffu, d_f, from);
       const int gy = __shfl_sync(0xffffffffu, d_y, from);
       const int gx = __shfl_sync(0xffffffffu, d_x, from);
-      if (tok < N) gc.rotate(row[i], c8, D, gf, gy, gx, rot);
+      if (tok < N) gc.rotate(row[i], c8, D, gf, gy, gx);
     }
     if (tok < N) {
 #pragma unroll

@@ -71,12 +71,43 @@ __device__ __forceinline__ void rotate8(Pack8<T>& x, int c8, int D, int f, int y
   }
 }
 
-// Without a cache kept by the caller.
+// Without a cache: straight-line code, every pair's angles are loaded (what the quantiser front ends use;
+// there the compare-and-skip of the cached form costs more than the loads it saves).
 template <typename T, int MODE>
 __device__ __forceinline__ void rotate8(Pack8<T>& x, int c8, int D, int f, int y, int xw,
                                         int F, int Hh, const RopeArgs& r) {
-  RotCache<MODE> cache;
-  rotate8<T, MODE>(x, c8, D, f, y, xw, F, Hh, r, cache);
+  using FT = typename RotCache<MODE>::F;
+  using FT2 = typename std::conditional<MODE == PARO_ROPE_REAL_F32, float2, double2>::type;
+  const int half = D >> 1;
+#pragma unroll
+  for (int p = 0; p < 4; ++p) {
+    const int pair = (c8 >> 1) + p;
+    const int row = pair < r.pairs_f ? f : (pair < r.pairs_f + r.pairs_h ? F + y : F + Hh + xw);
+    const size_t t = (size_t)row * half + pair;
+    FT c, s;
+    if (r.sin_tab == nullptr) {
+      const FT2 cs = static_cast<const FT2*>(r.cos_tab)[t];
+      c = cs.x; s = cs.y;
+    } else {
+      c = static_cast<const FT*>(r.cos_tab)[t];
+      s = static_cast<const FT*>(r.sin_tab)[t];
+    }
+    if constexpr (MODE == PARO_ROPE_REAL_F32) {
+      const float x0 = F16Traits<T>::to_float(x.e[2 * p]);
+      const float x1 = F16Traits<T>::to_float(x.e[2 * p + 1]);
+      const float o0 = __fadd_rn(__fmul_rn(x0, c), __fmul_rn(-x1, s));
+      const float o1 = __fadd_rn(__fmul_rn(x1, c), __fmul_rn(x0, s));
+      x.e[2 * p] = F16Traits<T>::from_float(o0);
+      x.e[2 * p + 1] = F16Traits<T>::from_float(o1);
+    } else {
+      const double x0 = (double)F16Traits<T>::to_float(x.e[2 * p]);
+      const double x1 = (double)F16Traits<T>::to_float(x.e[2 * p + 1]);
+      const double re = __dsub_rn(__dmul_rn(x0, c), __dmul_rn(x1, s));
+      const double im = __dadd_rn(__dmul_rn(x0, s), __dmul_rn(x1, c));
+      x.e[2 * p] = F16Traits<T>::from_float(__double2float_rn(re));
+      x.e[2 * p + 1] = F16Traits<T>::from_float(__double2float_rn(im));
+    }
+  }
 }
 
 }  // namespace paro
