@@ -106,6 +106,16 @@ __device__ __forceinline__ int ld_acquire_shared(const volatile int* ptr) {
 __device__ __forceinline__ void st_release_shared(volatile int* ptr, int v) {
   asm volatile("st.release.cta.shared.b32 [%0], %1;" ::"r"(umma::smem_u32(const_cast<int*>(ptr))), "r"(v) : "memory");
 }
+// The same by the lanes for which `pred` holds, as one predicated instruction (no divergent branch: see
+// umma::mbar_arrive_if).
+__device__ __forceinline__ void st_release_shared_if(volatile int* ptr, int v, bool pred) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %2, 0;\n\t"
+      "@p st.release.cta.shared.b32 [%0], %1;\n\t}"
+      ::"r"(umma::smem_u32(const_cast<int*>(ptr))), "r"(v), "r"((uint32_t)pred)
+      : "memory");
+}
 
 // One schedule entry = kbA | kbB << 16 (0xFFFF: no tile for that half in this step).  A step has one
 // MMA group of each kind per tile: group 0 serves the upper half, or both halves when the tile is

@@ -41,6 +41,16 @@ namespace paro {
 
 using namespace umma;
 
+// Developer aid, compiled out unless PARO_TRACE=<block index> is defined: that CTA of the fixed-reference
+// launch stamps clock64() at the hand-off points of its first 160 steps (roles: 0/1 K/V producer, 2/3
+// Q.K^T / P.V issuer, 4.. softmax warps; paro_debug_trace copies the table to the host).  This is how the
+// per-role time budget of a step was measured.
+#ifdef PARO_TRACE
+__device__ long long g_trace[16][160][8];
+#define TR(role, step, ev) do { if (FIXED && blockIdx.x == PARO_TRACE && (step) < 160) g_trace[role][step][ev] = clock64(); } while (0)
+#else
+#define TR(role, step, ev)
+#endif
 constexpr float RESCALE_TAU = 8.0f;            // exact walk: rescale O only when the row max grows by > 2^8
 constexpr float REF_OFFSET = 20.f;             // fixed reference: the first block's maximum maps to P = 2^-20
 constexpr float ROWSUM_LIMIT = 1.2676506e30f;  // 2^100: a step's row sum beyond it gives the pair back
@@ -188,12 +198,14 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
         for (int j = 0; j < 2; ++j) {
           if (!act_[j]) continue;
           const int st = t % KST, use = t / KST;
+          TR(0, i, 2 * j);
           if (use > 0 && !mbar_wait_bounded(bar_kfree + st, (use - 1) & 1, abort_flag, WAIT_LIMIT)) {
             report_timeout(p, abort_flag, 1, i);
             ok = false;
             break;
           }
           ++t;
+          TR(0, i, 2 * j + 1);
           mbar_arrive_expect_tx(bar_kfull + st, Cfg::K_BYTES);
           tma_load_3d(sK + st * Cfg::K_BYTES, &tm_k, 0, kblk_[j] * 64, bh, bar_kfull + st);
         }
@@ -214,12 +226,14 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
         for (int j = 0; j < 2; ++j) {
           if (!act_[j]) continue;
           const int st = t % VST, use = t / VST;
+          TR(1, i, 2 * j);
           if (use > 0 && !mbar_wait_bounded(bar_vfree + st, (use - 1) & 1, abort_flag, WAIT_LIMIT)) {
             report_timeout(p, abort_flag, 9, i);
             ok = false;
             break;
           }
           ++t;
+          TR(1, i, 2 * j + 1);
           mbar_arrive_expect_tx(bar_vfull + st, Cfg::V_BYTES);
           tma_load_3d(sV + st * Cfg::V_BYTES, &tm_v, kblk_[j] * 64, 0, bh, bar_vfull + st);
         }
@@ -230,44 +244,72 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
       // ---------------------------------------------------------------- MMA issuer: S = Q.K^T
       // (the two issuers are separate threads so that a P.V group waiting for room in the tensor
       // queue does not hold back the next scores, and vice versa)
+      // Each issuer is one thread running dependent scalar code next to the softmax warps, and every
+      // tile of the walk passes through it, so its instruction count per tile is on the kernel's
+      // critical path.  Hence: barrier addresses and the stage-0 descriptor are formed once, the
+      // polls of a tile's barriers are issued together, ring position and phase are counters, and the
+      // lane masks are compile-time constants of three instantiations of the tile code (W = 0 upper
+      // half, 1 lower half, 2 both halves, unmasked form).
       constexpr uint32_t IDESC_QK = instr_desc(2, 1, 1, 128, 64);  // s32 += s8 * s8
       do {
         ATT_WAIT(bar_q, 0, 2, -1)
-        bool ok = true;
-        int t = 0;
+        const uint32_t a_sfree = smem_u32(bar_sfree), a_sready = smem_u32(bar_sready);
+        const uint32_t a_kfull = smem_u32(bar_kfull), a_kfree = smem_u32(bar_kfree);
+        const uint64_t dK0 = smem_desc(smem_u32(sK), D);
+        uint32_t st = 0, kph = 0;   // ring stage of the next tile and the parity of its current use
+        auto tile = [&](auto wtag, const int i, const int ev) -> bool {
+          constexpr int W = decltype(wtag)::value;
+          // the scores of step i-1 of the halves served are in registers: their rows of S may be
+          // overwritten.  (i = 0 asks an unused barrier for parity 1, which passes at once.)
+          const uint32_t par = (uint32_t)(i - 1) & 1u, ph = ((uint32_t)(i - 1) >> 1) & 1u;
+          TR(2, i, ev + 0);
+          const bool r0 = W == 1 || mbar_poll(a_sfree + 8u * par, ph);
+          const bool r1 = W == 0 || mbar_poll(a_sfree + 16u + 8u * par, ph);
+          const bool r2 = mbar_poll(a_kfull + 8u * st, kph);
+          if (!(r0 && r1 && r2)) {
+            bool good = true;
+            if (W != 1) good = mbar_wait_bounded(bar_sfree + par, ph, abort_flag, WAIT_LIMIT);
+            if (W != 0) good = good && mbar_wait_bounded(bar_sfree + 2 + par, ph, abort_flag, WAIT_LIMIT);
+            good = good && mbar_wait_bounded(bar_kfull + st, kph, abort_flag, WAIT_LIMIT);
+            if (!good) return false;
+          }
+          TR(2, i, ev + 1);
+          tc_fence_after();
+          const uint64_t dK = dK0 + (uint64_t)(st * (uint32_t)(Cfg::K_BYTES >> 4));
+#pragma unroll
+          for (int k = 0; k < D / 32; ++k) {
+            if (W == 2) mma_i8_ts(tS, tQ + 8 * k, desc_advance(dK, 32 * k), IDESC_QK, k > 0);
+            else if (W == 0)   // lanes NOT written: the rows of the half the tile does not serve
+              mma_i8_ts_masked(tS, tQ + 8 * k, desc_advance(dK, 32 * k), IDESC_QK, k > 0, 0u, 0u, 0xffffffffu, 0xffffffffu);
+            else
+              mma_i8_ts_masked(tS, tQ + 8 * k, desc_advance(dK, 32 * k), IDESC_QK, k > 0, 0xffffffffu, 0xffffffffu, 0u, 0u);
+          }
+          mma_commit_at(a_kfree + 8u * st);
+          TR(2, i, ev + 2);
+          if (W != 1) mma_commit_at(a_sready + 8u * (uint32_t)(i & 1));
+          if (W != 0) mma_commit_at(a_sready + 16u + 8u * (uint32_t)(i & 1));
+          if (++st == KST) {
+            st = 0;
+            kph ^= 1u;
+          }
+          TR(2, i, ev + 3);
+          return true;
+        };
         uint32_t e_cur = n_steps > 0 ? sched[0] : 0u, e_nxt = n_steps > 1 ? sched[1] : 0u;
-        for (int i = 0; i < n_steps && ok; ++i) {
-          PARO_STEP_GROUPS(e_cur)
+        for (int i = 0; i < n_steps; ++i) {
+          const uint32_t ka = e_cur & 0xFFFFu, kb = e_cur >> 16;
           e_cur = e_nxt;
           if (i + 2 < n_steps) e_nxt = ld_pinned_u32(sched + i + 2);
-#pragma unroll
-          for (int j = 0; j < 2; ++j) {   // one MMA group per tile; lane-masked unless it serves both halves
-            if (!act_[j]) continue;
-            const int w = which_[j], st = t % KST, use = t / KST;
-            ++t;
-            // the scores of step i-1 of the halves served are in registers: their rows of S may be overwritten
-            bool good = true;
-            if (i > 0) {
-              const int par = (i - 1) & 1, ph = ((i - 1) >> 1) & 1;
-              if (w != 1) good = good && mbar_wait_bounded(bar_sfree + par, ph, abort_flag, WAIT_LIMIT);
-              if (w != 0) good = good && mbar_wait_bounded(bar_sfree + 2 + par, ph, abort_flag, WAIT_LIMIT);
-            }
-            good = good && mbar_wait_bounded(bar_kfull + st, use & 1, abort_flag, WAIT_LIMIT);
-            if (!good) {
-              report_timeout(p, abort_flag, 3, i);
-              ok = false;
-              break;
-            }
-            tc_fence_after();
-            const uint64_t dK = smem_desc(smem_u32(sK + st * Cfg::K_BYTES), D);
-            // lanes NOT written: the rows of a half the tile does not serve
-            const uint32_t lo = w == 1 ? 0xffffffffu : 0u, hi = w == 0 ? 0xffffffffu : 0u;
-#pragma unroll
-            for (int k = 0; k < D / 32; ++k)
-              mma_i8_ts_masked(tS, tQ + 8 * k, desc_advance(dK, 32 * k), IDESC_QK, k > 0, lo, lo, hi, hi);
-            mma_commit(bar_kfree + st);
-            if (w != 1) mma_commit(bar_sready + (i & 1));
-            if (w != 0) mma_commit(bar_sready + 2 + (i & 1));
+          bool good;
+          if (SHARE_TILES && ka == kb && ka != 0xFFFFu) {
+            good = tile(std::integral_constant<int, 2>{}, i, 0);
+          } else {
+            good = ka == 0xFFFFu || tile(std::integral_constant<int, 0>{}, i, 0);
+            good = good && (kb == 0xFFFFu || tile(std::integral_constant<int, 1>{}, i, 4));
+          }
+          if (!good) {
+            report_timeout(p, abort_flag, 3, i);
+            break;
           }
         }
       } while (false);
@@ -278,39 +320,64 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
     } else if (warp == 11 && lane == 0) {
       // ---------------------------------------------------------------- MMA issuer: O += P.V
       constexpr uint32_t IDESC_PV = instr_desc(1, 1, 1, 128, D);   // f32 += bf16 * bf16
-      bool ok = true;
-      int t = 0;
+      const uint32_t a_pready = smem_u32(bar_pready), a_pvdone = smem_u32(bar_pvdone);
+      const uint32_t a_vfull = smem_u32(bar_vfull), a_vfree = smem_u32(bar_vfree);
+      const uint64_t dV0 = smem_desc(smem_u32(sV), 128);
+      uint32_t st = 0, vph = 0;
+      auto tile = [&](auto wtag, const int i, const int ev) -> bool {
+        constexpr int W = decltype(wtag)::value;
+        const uint32_t par = (uint32_t)i & 1u, ph = ((uint32_t)i >> 1) & 1u;
+        TR(3, i, ev + 0);
+        const bool r0 = W == 1 || mbar_poll(a_pready + 8u * par, ph);
+        const bool r1 = W == 0 || mbar_poll(a_pready + 16u + 8u * par, ph);
+        const bool r2 = mbar_poll(a_vfull + 8u * st, vph);
+        if (!(r0 && r1 && r2)) {
+          bool good = true;
+          if (W != 1) good = mbar_wait_bounded(bar_pready + par, ph, abort_flag, WAIT_LIMIT);
+          if (W != 0) good = good && mbar_wait_bounded(bar_pready + 2 + par, ph, abort_flag, WAIT_LIMIT);
+          good = good && mbar_wait_bounded(bar_vfull + st, vph, abort_flag, WAIT_LIMIT);
+          if (!good) return false;
+        }
+        TR(3, i, ev + 1);
+        tc_fence_after();
+        const uint64_t dV = dV0 + (uint64_t)(st * (uint32_t)(Cfg::V_BYTES >> 4));
+        // both halves start at step 0, so a tile that serves both never mixes a first with a later step
+        const uint32_t acc0 = i > 0 ? 1u : 0u;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const uint32_t acc = k > 0 ? 1u : acc0;
+          if (W == 2) mma_f16_ts(tO, tP + 8 * k, desc_advance(dV, 32 * k), IDESC_PV, acc);
+          else if (W == 0)
+            mma_f16_ts_masked(tO, tP + 8 * k, desc_advance(dV, 32 * k), IDESC_PV, acc, 0u, 0u, 0xffffffffu, 0xffffffffu);
+          else
+            mma_f16_ts_masked(tO, tP + 8 * k, desc_advance(dV, 32 * k), IDESC_PV, acc, 0xffffffffu, 0xffffffffu, 0u, 0u);
+        }
+        mma_commit_at(a_vfree + 8u * st);
+        TR(3, i, ev + 2);
+        if (W != 1) mma_commit_at(a_pvdone + 8u * par);
+        if (W != 0) mma_commit_at(a_pvdone + 16u + 8u * par);
+        if (++st == VST) {
+          st = 0;
+          vph ^= 1u;
+        }
+        TR(3, i, ev + 3);
+        return true;
+      };
       uint32_t e_cur = n_steps > 0 ? sched[0] : 0u, e_nxt = n_steps > 1 ? sched[1] : 0u;
-      for (int i = 0; i < n_steps && ok; ++i) {
-        PARO_STEP_GROUPS(e_cur)
+      for (int i = 0; i < n_steps; ++i) {
+        const uint32_t ka = e_cur & 0xFFFFu, kb = e_cur >> 16;
         e_cur = e_nxt;
         if (i + 2 < n_steps) e_nxt = ld_pinned_u32(sched + i + 2);
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-          if (!act_[j]) continue;
-          const int w = which_[j], st = t % VST, use = t / VST;
-          ++t;
-          const int par = i & 1, ph = (i >> 1) & 1;
-          bool good = true;
-          if (w != 1) good = good && mbar_wait_bounded(bar_pready + par, ph, abort_flag, WAIT_LIMIT);
-          if (w != 0) good = good && mbar_wait_bounded(bar_pready + 2 + par, ph, abort_flag, WAIT_LIMIT);
-          good = good && mbar_wait_bounded(bar_vfull + st, use & 1, abort_flag, WAIT_LIMIT);
-          if (!good) {
-            report_timeout(p, abort_flag, 5, i);
-            ok = false;
-            break;
-          }
-          tc_fence_after();
-          const uint64_t dV = smem_desc(smem_u32(sV + st * Cfg::V_BYTES), 128);
-          const uint32_t lo = w == 1 ? 0xffffffffu : 0u, hi = w == 0 ? 0xffffffffu : 0u;
-          // both halves start at step 0, so a tile that serves both never mixes a first with a later step
-#pragma unroll
-          for (int k = 0; k < 4; ++k)
-            mma_f16_ts_masked(tO, tP + 8 * k, desc_advance(dV, 32 * k), IDESC_PV, (i > 0 || k > 0) ? 1u : 0u, lo, lo, hi,
-                              hi);
-          mma_commit(bar_vfree + st);
-          if (w != 1) mma_commit(bar_pvdone + par);
-          if (w != 0) mma_commit(bar_pvdone + 2 + par);
+        bool good;
+        if (SHARE_TILES && ka == kb && ka != 0xFFFFu) {
+          good = tile(std::integral_constant<int, 2>{}, i, 0);
+        } else {
+          good = ka == 0xFFFFu || tile(std::integral_constant<int, 0>{}, i, 0);
+          good = good && (kb == 0xFFFFu || tile(std::integral_constant<int, 1>{}, i, 4));
+        }
+        if (!good) {
+          report_timeout(p, abort_flag, 5, i);
+          break;
         }
       }
       if (*abort_flag) {
@@ -348,7 +415,7 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar_q);
+      mbar_arrive_if(bar_q, lane == 0);
     }
     const int per_bh = p.nb * (64 / p.q_group);
     // rows past the end of the sequence: scale 0, or (fixed reference) a tiny positive one -- there the
@@ -385,17 +452,25 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
         kb_next = min(my_kb(i + 2), p.nb - 1);
         ks_next = kscale_bh[kb_next];
       }
+      [[maybe_unused]] const int trole = 4 + warp;
+      TR(trole, i, 0);
       if (!wait_bar(my_sready, i >> 1, 6, i)) return false;
+      TR(trole, i, 1);
       float f[64];
       {
         uint32_t s[64];
         tmem_ld32(tS + lane_off, s);
         tmem_ld32(tS + lane_off + 32u, s + 32);
         tmem_wait_ld();
+        TR(trole, i, 2);
         // the scores are in registers: let the issuer overwrite S with this half's next step
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(my_sfree);
+        mbar_arrive_if(my_sfree, lane == 0);
+        // A branch on a value read after the arrival ends the basic block here.  Without it the
+        // arrival, which nothing below depends on, is scheduled at the END of the straight-line code
+        // that follows (after the step's exponentials), and the next Q.K^T starts that much later.
+        if (*abort_flag) return false;
         // int32 scores -> fp32 by an integer addition instead of a conversion: the bit pattern
         // 0x4B400000 + s is the float SCORE_BIAS + s exactly (|s| <= 127 * 127 * D < 2^22).  The bias is
         // monotonic, so the row maximum is taken over the biased values, and it is folded into the
@@ -431,7 +506,7 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
           m_ref = row_max() + REF_OFFSET;
           s_mrow[r] = m_ref;
           __syncwarp();
-          if (lane == 0) st_release_shared(s_mstep + qd, 1);
+          st_release_shared_if(s_mstep + qd, 1, lane == 0);
         } else if (FIRST) {   // (step 1) the other warp set fixed the reference in step 0
           bool seen = ld_acquire_shared(s_mstep + qd) != 0;
           if (!seen) {
@@ -474,7 +549,7 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
       }
       s_mrow[r] = m_new;
       __syncwarp();
-      if (lane == 0) st_release_shared(s_mstep + qd, i + 1);
+      st_release_shared_if(s_mstep + qd, i + 1, lane == 0);
       if (m_new != m_l) {
         l *= ex2_approx(m_l - m_new);     // 0 when m_l = -inf
         m_l = m_new;
@@ -500,22 +575,22 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
       const float xoff = fmaf(-SCORE_BIAS, sc, -m_new);   // (bias + s) * sc + xoff = s * sc - m
       const uint64_t sc2 = pack2(sc, sc), negm2 = pack2(xoff, xoff);
       uint64_t sum2[2] = {0ull, 0ull};
+      uint32_t pk[32];   // bf16 P: two values per 32-bit column
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t pk[16];
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          float x0, x1;
-          unpack2(fma2(pack2(f[32 * c + 2 * j], f[32 * c + 2 * j + 1]), sc2, negm2), x0, x1);
-          const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);   // 2^-inf = 0 for masked columns
-          sum2[j & 1] = add2(sum2[j & 1], pack2(p0, p1));
-          pk[j] = pack_bf16x2(p0, p1);
-        }
-        // P of this half is rewritten only after the P.V that read its previous contents (the other
-        // warp set's step) has finished
-        if (c == 0 && !pv_consumed && !wait_bar(prev_pvdone, (i - 1) >> 1, 7, i)) return false;
-        tmem_st16(tP + lane_off + 16 * c, pk);   // bf16 P: two values per 32-bit column
+      for (int j = 0; j < 32; ++j) {
+        float x0, x1;
+        unpack2(fma2(pack2(f[2 * j], f[2 * j + 1]), sc2, negm2), x0, x1);
+        const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);   // 2^-inf = 0 for masked columns
+        sum2[j & 1] = add2(sum2[j & 1], pack2(p0, p1));
+        pk[j] = pack_bf16x2(p0, p1);
       }
+      // P of this half is rewritten only after the P.V that read its previous contents (the other warp
+      // set's step) has finished.  All of the step's arithmetic is done by now: between that P.V's
+      // completion and this step's P being ready for the issuer lie one store and one arrival.
+      TR(trole, i, 3);
+      if (!pv_consumed && !wait_bar(prev_pvdone, (i - 1) >> 1, 7, i)) return false;
+      TR(trole, i, 4);
+      tmem_st32(tP + lane_off, pk);
       float sa, sb;
       unpack2(add2(sum2[0], sum2[1]), sa, sb);
       if constexpr (FIXED) redo = redo || !(sa + sb < ROWSUM_LIMIT);   // out of range, or NaN
@@ -527,7 +602,8 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(my_pready);   // one arrival per warp
+      mbar_arrive_if(my_pready, lane == 0);   // one arrival per warp
+      TR(trole, i, 5);
       return true;
     };
     if constexpr (FIXED) {
@@ -742,3 +818,9 @@ extern "C" int paro_status_poll(const int32_t* status, int32_t* host_out, paro_s
     return fail(PARO_ETIMEOUT, "sparse attention wait expired: role %d, work item %d, tile %d", w[1], w[2], w[3]);
   return PARO_OK;
 }
+
+#ifdef PARO_TRACE
+extern "C" int paro_debug_trace(long long* host_out) {
+  return cudaMemcpyFromSymbol(host_out, paro::g_trace, sizeof(paro::g_trace)) == cudaSuccess ? 0 : -1;
+}
+#endif

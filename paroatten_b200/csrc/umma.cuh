@@ -24,6 +24,18 @@ __device__ __forceinline__ void fence_proxy_async() {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// Arrival by the lanes for which `pred` holds, as ONE predicated instruction.  (Written as
+// `if (lane == 0) mbar_arrive(bar)` the arrival sits in a divergent branch: the other 31 lanes run on
+// through the code that follows and the arriving lane is only scheduled when they reach their next
+// warp-synchronous instruction, so the barrier completes that much later.)
+__device__ __forceinline__ void mbar_arrive_if(uint64_t* bar, bool pred) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %1, 0;\n\t"
+      "@p mbarrier.arrive.shared::cta.b64 _, [%0];\n\t}"
+      ::"r"(smem_u32(bar)), "r"((uint32_t)pred)
+      : "memory");
+}
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
                : "memory");
@@ -49,6 +61,20 @@ __device__ __forceinline__ bool mbar_try_wait_suspend(uint64_t* bar, uint32_t pa
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
       : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
+
+// One poll by shared-memory address (no suspension): callers that hold several barriers' addresses in
+// registers issue their polls back to back, so that the polls' latencies overlap.
+__device__ __forceinline__ bool mbar_poll(uint32_t bar_saddr, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar_saddr), "r"(parity)
       : "memory");
   return ok != 0;
 }
@@ -232,6 +258,11 @@ __device__ __forceinline__ void mma_f16_ts_masked(uint32_t d_tmem, uint32_t a_tm
 // Arrives once on `bar` when every tcgen05.mma issued so far by this thread has completed.
 __device__ __forceinline__ void mma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+
+__device__ __forceinline__ void mma_commit_at(uint32_t bar_saddr) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_saddr)
                : "memory");
 }
 
