@@ -117,6 +117,22 @@ __device__ __forceinline__ void st_release_shared_if(volatile int* ptr, int v, b
       : "memory");
 }
 
+// What a ring producer remembers about the last S tiles it loaded, oldest first: the commit barrier that
+// tells when the MMAs reading the tile have finished (shared-memory address | phase parity << 31).
+// Before it reuses a stage, the producer waits on the oldest entry -- the tile that holds that stage.
+template <int S> struct ReleaseFifo {
+  uint32_t tok[S];
+  __device__ __forceinline__ uint32_t oldest() const { return tok[0]; }
+  __device__ __forceinline__ void push(uint32_t v) {
+#pragma unroll
+    for (int k = 0; k + 1 < S; ++k) tok[k] = tok[k + 1];
+    tok[S - 1] = v;
+  }
+};
+__device__ __forceinline__ uint32_t commit_token(uint32_t bars_saddr, int half, int step) {
+  return (bars_saddr + 32u * (uint32_t)half + 8u * ((uint32_t)step & 3u)) | ((((uint32_t)step >> 2) & 1u) << 31);
+}
+
 // One schedule entry = kbA | kbB << 16 (0xFFFF: no tile for that half in this step).  A step has one
 // MMA group of each kind per tile: group 0 serves the upper half, or both halves when the tile is
 // shared (kbA == kbB and SHARE); group 1 serves the lower half.

@@ -59,8 +59,13 @@ template <int D> struct AttnCfg {
   // Ring depths.  TMEM allows two CTAs per SM; the loads run far ahead of their use at any depth from 2
   // to 6 (same time within noise), so the rings are kept short and the shared memory left over is
   // requested back as L1 (carve-out attribute at launch) for the schedule entries and k-block scales.
-  static constexpr int K_STAGES = (D == 128) ? 3 : 6;
-  static constexpr int V_STAGES = (D == 128) ? 3 : 5;
+  static constexpr int K_STAGES = (D == 128) ? 3 : 4;
+  static constexpr int V_STAGES = (D == 128) ? 3 : 4;
+  // The commit barriers are indexed by step modulo STEP_BARS, and a ring stage is handed back to its
+  // producer through the commit barrier of the tile that used it: a producer can only tell that
+  // barrier's phases apart while the ring is no deeper than STEP_BARS.
+  static constexpr int STEP_BARS = 4;
+  static_assert(K_STAGES <= STEP_BARS && V_STAGES <= STEP_BARS, "ring deeper than the commit barriers can tell apart");
   static constexpr int K_BYTES = 64 * D;
   static constexpr int V_BYTES = D * 128;   // D rows of 64 bf16
   static constexpr int TILE_BYTES = K_STAGES * K_BYTES + V_STAGES * V_BYTES;
@@ -99,14 +104,14 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
   // barrier is arrived on and waited for by the same parties in every phase.
   uint64_t* bar_q = reinterpret_cast<uint64_t*>(aux);   // [1]     Q tile stored in TMEM
   uint64_t* bar_kfull = bar_q + 1;                      // [KST]   K tile landed
-  uint64_t* bar_kfree = bar_kfull + KST;                // [KST]   the Q.K^T that read the K stage finished
-  uint64_t* bar_vfull = bar_kfree + KST;                // [VST]   V tile landed
-  uint64_t* bar_vfree = bar_vfull + VST;                // [VST]   the P.V that read the V stage finished
-  uint64_t* bar_sready = bar_vfree + VST;               // [2][2]  scores of (half, step parity) in TMEM
-  uint64_t* bar_sfree = bar_sready + 4;                 // [2][2]  ... copied to registers
+  uint64_t* bar_vfull = bar_kfull + KST;                // [VST]   V tile landed
+  uint64_t* bar_sready = bar_vfull + VST;               // [2][4]  scores of (half, step mod 4) in TMEM: the Q.K^T
+                                                        //         finished, so its K stage is free as well
+  uint64_t* bar_pvdone = bar_sready + 8;                // [2][4]  P.V of (half, step mod 4) finished: P may be
+                                                        //         rewritten, the V stage is free
+  uint64_t* bar_sfree = bar_pvdone + 8;                 // [2][2]  scores of (half, step parity) copied to registers
   uint64_t* bar_pready = bar_sfree + 4;                 // [2][2]  P of (half, step parity) written
-  uint64_t* bar_pvdone = bar_pready + 4;                // [2][2]  P.V of (half, step parity) finished
-  uint64_t* bar_drain = bar_pvdone + 4;                 // [2]     issuers' MMAs retired (abort path only)
+  uint64_t* bar_drain = bar_pready + 4;                 // [2]     issuers' MMAs retired (abort path only)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_drain + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* s_drain = abort_flag + 1;                  // 1: an earlier launch or CTA failed, leave at once
@@ -117,7 +122,7 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
   volatile float* s_mrow = reinterpret_cast<volatile float*>(aux + 1536);   // [128] running row maximum
   float* s_xl = reinterpret_cast<float*>(aux + 2048);                       // [2][128] row-sum exchange
   static_assert(512 + 2 * D * 4 <= 1536 && 2048 + 2 * 128 * 4 <= Cfg::AUX_BYTES, "aux area too small");
-  static_assert((19 + 2 * KST + 2 * VST) * 8 + 8 + 28 <= 512, "barrier area too small");
+  static_assert((27 + KST + VST) * 8 + 8 + 28 <= 512, "barrier area too small");
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // one thread decides for the whole CTA whether an earlier failure makes this launch drain (every
@@ -150,19 +155,15 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
 
   if (threadIdx.x == 0) {
     mbar_init(bar_q, 4);
-    for (int i = 0; i < KST; ++i) {
-      mbar_init(bar_kfull + i, 1);
-      mbar_init(bar_kfree + i, 1);
-    }
-    for (int i = 0; i < VST; ++i) {
-      mbar_init(bar_vfull + i, 1);
-      mbar_init(bar_vfree + i, 1);
+    for (int i = 0; i < KST; ++i) mbar_init(bar_kfull + i, 1);
+    for (int i = 0; i < VST; ++i) mbar_init(bar_vfull + i, 1);
+    for (int i = 0; i < 8; ++i) {
+      mbar_init(bar_sready + i, 1);
+      mbar_init(bar_pvdone + i, 1);
     }
     for (int i = 0; i < 4; ++i) {
-      mbar_init(bar_sready + i, 1);
       mbar_init(bar_sfree + i, 2);    // the two warps (lane quadrants) of a half in one warp set
       mbar_init(bar_pready + i, 2);
-      mbar_init(bar_pvdone + i, 1);
       s_mstep[i] = 0;
     }
     mbar_init(bar_drain, 1);
@@ -188,6 +189,10 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
       tma_prefetch_desc(&tm_k);
       bool ok = true;
       int t = 0;   // tiles so far = position in the ring
+      // a stage is free again when the Q.K^T of the tile that held it has finished: the scores-ready
+      // commit of that tile (no commit of its own for the ring)
+      const uint32_t a_done = smem_u32(bar_sready);
+      ReleaseFifo<KST> held;
       // schedule entries are fetched two steps ahead of their use
       uint32_t e_cur = n_steps > 0 ? sched[0] : 0u, e_nxt = n_steps > 1 ? sched[1] : 0u;
       for (int i = 0; i < n_steps && ok; ++i) {
@@ -197,13 +202,14 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
           if (!act_[j]) continue;
-          const int st = t % KST, use = t / KST;
+          const int st = t % KST;
           TR(0, i, 2 * j);
-          if (use > 0 && !mbar_wait_bounded(bar_kfree + st, (use - 1) & 1, abort_flag, WAIT_LIMIT)) {
+          if (t >= KST && !mbar_wait_bounded_at(held.oldest() & 0x7fffffffu, held.oldest() >> 31, abort_flag, WAIT_LIMIT)) {
             report_timeout(p, abort_flag, 1, i);
             ok = false;
             break;
           }
+          held.push(commit_token(a_done, j, i));   // (a tile shared by both halves commits to both: j = 0 is watched)
           ++t;
           TR(0, i, 2 * j + 1);
           mbar_arrive_expect_tx(bar_kfull + st, Cfg::K_BYTES);
@@ -217,6 +223,8 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
       tma_prefetch_desc(&tm_v);
       bool ok = true;
       int t = 0;
+      const uint32_t a_done = smem_u32(bar_pvdone);   // the P.V commit of the tile that held the stage
+      ReleaseFifo<VST> held;
       uint32_t e_cur = n_steps > 0 ? sched[0] : 0u, e_nxt = n_steps > 1 ? sched[1] : 0u;
       for (int i = 0; i < n_steps && ok; ++i) {
         PARO_STEP_GROUPS(e_cur)
@@ -225,13 +233,14 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
           if (!act_[j]) continue;
-          const int st = t % VST, use = t / VST;
+          const int st = t % VST;
           TR(1, i, 2 * j);
-          if (use > 0 && !mbar_wait_bounded(bar_vfree + st, (use - 1) & 1, abort_flag, WAIT_LIMIT)) {
+          if (t >= VST && !mbar_wait_bounded_at(held.oldest() & 0x7fffffffu, held.oldest() >> 31, abort_flag, WAIT_LIMIT)) {
             report_timeout(p, abort_flag, 9, i);
             ok = false;
             break;
           }
+          held.push(commit_token(a_done, j, i));
           ++t;
           TR(1, i, 2 * j + 1);
           mbar_arrive_expect_tx(bar_vfull + st, Cfg::V_BYTES);
@@ -254,7 +263,7 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
       do {
         ATT_WAIT(bar_q, 0, 2, -1)
         const uint32_t a_sfree = smem_u32(bar_sfree), a_sready = smem_u32(bar_sready);
-        const uint32_t a_kfull = smem_u32(bar_kfull), a_kfree = smem_u32(bar_kfree);
+        const uint32_t a_kfull = smem_u32(bar_kfull);
         const uint64_t dK0 = smem_desc(smem_u32(sK), D);
         uint32_t st = 0, kph = 0;   // ring stage of the next tile and the parity of its current use
         auto tile = [&](auto wtag, const int i, const int ev) -> bool {
@@ -284,10 +293,10 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
             else
               mma_i8_ts_masked(tS, tQ + 8 * k, desc_advance(dK, 32 * k), IDESC_QK, k > 0, 0xffffffffu, 0xffffffffu, 0u, 0u);
           }
-          mma_commit_at(a_kfree + 8u * st);
           TR(2, i, ev + 2);
-          if (W != 1) mma_commit_at(a_sready + 8u * (uint32_t)(i & 1));
-          if (W != 0) mma_commit_at(a_sready + 16u + 8u * (uint32_t)(i & 1));
+          // one commit per half served: the softmax warps wait on it for the scores, the K producer for the stage
+          if (W != 1) mma_commit_at(a_sready + 8u * (uint32_t)(i & 3));
+          if (W != 0) mma_commit_at(a_sready + 32u + 8u * (uint32_t)(i & 3));
           if (++st == KST) {
             st = 0;
             kph ^= 1u;
@@ -321,7 +330,7 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
       // ---------------------------------------------------------------- MMA issuer: O += P.V
       constexpr uint32_t IDESC_PV = instr_desc(1, 1, 1, 128, D);   // f32 += bf16 * bf16
       const uint32_t a_pready = smem_u32(bar_pready), a_pvdone = smem_u32(bar_pvdone);
-      const uint32_t a_vfull = smem_u32(bar_vfull), a_vfree = smem_u32(bar_vfree);
+      const uint32_t a_vfull = smem_u32(bar_vfull);
       const uint64_t dV0 = smem_desc(smem_u32(sV), 128);
       uint32_t st = 0, vph = 0;
       auto tile = [&](auto wtag, const int i, const int ev) -> bool {
@@ -352,10 +361,9 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
           else
             mma_f16_ts_masked(tO, tP + 8 * k, desc_advance(dV, 32 * k), IDESC_PV, acc, 0xffffffffu, 0xffffffffu, 0u, 0u);
         }
-        mma_commit_at(a_vfree + 8u * st);
         TR(3, i, ev + 2);
-        if (W != 1) mma_commit_at(a_pvdone + 8u * par);
-        if (W != 0) mma_commit_at(a_pvdone + 16u + 8u * par);
+        if (W != 1) mma_commit_at(a_pvdone + 8u * (uint32_t)(i & 3));
+        if (W != 0) mma_commit_at(a_pvdone + 32u + 8u * (uint32_t)(i & 3));
         if (++st == VST) {
           st = 0;
           vph ^= 1u;
@@ -426,16 +434,15 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
     // (exact walk) or to the row's fixed reference exponent m_ref
     float m_l = -INFINITY, l = 0.f, m_ref = 0.f;
     bool ok = true, redo = false;
-    auto wait_bar = [&](uint64_t* bar, int phase, int code, int i) {
-      const bool good = __all_sync(0xffffffffu, mbar_wait_bounded(bar, phase & 1, abort_flag, WAIT_LIMIT));
+    auto wait_bar = [&](uint32_t bar_saddr, int phase, int code, int i) {
+      const bool good = __all_sync(0xffffffffu, mbar_wait_bounded_at(bar_saddr, phase & 1, abort_flag, WAIT_LIMIT));
       if (!good) report_timeout(p, abort_flag, code, i);
       tc_fence_after();
       return good;
     };
-    uint64_t* const my_sready = bar_sready + 2 * half + set;
     uint64_t* const my_sfree = bar_sfree + 2 * half + set;
     uint64_t* const my_pready = bar_pready + 2 * half + set;
-    uint64_t* const prev_pvdone = bar_pvdone + 2 * half + (set ^ 1);   // P.V of the steps of the other parity
+    const uint32_t my_sready = smem_u32(bar_sready + 4 * half), my_pvdone = smem_u32(bar_pvdone + 4 * half);   // [step mod 4]
     const float* kscale_bh = p.k_scale + (size_t)bh * p.nb;
     // (a k-block id beyond the sequence can only come from a malformed plan; clamped so that the scale
     // look-up stays inside its array)
@@ -454,7 +461,7 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
       }
       [[maybe_unused]] const int trole = 4 + warp;
       TR(trole, i, 0);
-      if (!wait_bar(my_sready, i >> 1, 6, i)) return false;
+      if (!wait_bar(my_sready + 8u * (i & 3), i >> 2, 6, i)) return false;
       TR(trole, i, 1);
       float f[64];
       {
@@ -556,7 +563,7 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
       }
       if (__any_sync(0xffffffffu, resc)) {  // O may only be touched once this half's previous P.V has landed
         pv_consumed = true;
-        if (!wait_bar(prev_pvdone, (i - 1) >> 1, 7, i)) return false;
+        if (!wait_bar(my_pvdone + 8u * ((i - 1) & 3), (i - 1) >> 2, 7, i)) return false;
         const float alpha = resc ? ex2_approx(m_old - m_new) : 1.f;
         // (rare, and deliberately not unrolled: unrolled, this loop costs the hot path 19 spilled registers)
 #pragma unroll 1
@@ -588,7 +595,7 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
       // set's step) has finished.  All of the step's arithmetic is done by now: between that P.V's
       // completion and this step's P being ready for the issuer lie one store and one arrival.
       TR(trole, i, 3);
-      if (!pv_consumed && !wait_bar(prev_pvdone, (i - 1) >> 1, 7, i)) return false;
+      if (!pv_consumed && !wait_bar(my_pvdone + 8u * ((i - 1) & 3), (i - 1) >> 2, 7, i)) return false;
       TR(trole, i, 4);
       tmem_st32(tP + lane_off, pk);
       float sa, sb;
@@ -615,7 +622,7 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
 
     // epilogue (the TMEM loads are warp-collective: every lane of the warp executes them, rows past
     // the end of the sequence only skip the store)
-    if (ok && n_mine > 0) ok = wait_bar(bar_pvdone + 2 * half + ((n_mine - 1) & 1), (n_mine - 1) >> 1, 8, n_mine);
+    if (ok && n_mine > 0) ok = wait_bar(my_pvdone + 8u * ((n_mine - 1) & 3), (n_mine - 1) >> 2, 8, n_mine);
     // final maximum and row sum = both threads' shares (reached by every softmax thread, also
     // after a failed wait)
     if (FIXED && redo) *s_redo = 1;

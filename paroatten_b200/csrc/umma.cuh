@@ -93,6 +93,26 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
   return true;
 }
 
+// The same for a barrier given by its shared-memory address.
+__device__ __forceinline__ bool mbar_wait_bounded_at(uint32_t bar_saddr, uint32_t parity, volatile int* abort_flag,
+                                                     long long limit_cycles) {
+  if (mbar_poll(bar_saddr, parity)) return true;
+  const long long t0 = clock64();
+  for (;;) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar_saddr), "r"(parity), "r"(20000u)
+        : "memory");
+    if (ok) return true;
+    if (*abort_flag) return false;
+    if (clock64() - t0 > limit_cycles) return false;
+  }
+}
+
 // The same without an abort flag: used by a role that is already leaving and only has to see its own
 // copies or MMAs retire before the CTA's shared and tensor memory are handed on.
 __device__ __forceinline__ bool mbar_wait_plain_bounded(uint64_t* bar, uint32_t parity, long long limit_cycles) {
