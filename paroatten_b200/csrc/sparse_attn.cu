@@ -146,6 +146,10 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
   // is not what limits the kernel and the wait costs 13 % on the CogVideoX shape, so tiles are only
   // shared at D = 128.
   constexpr bool SHARE_TILES = (D == 128);
+  // At D = 128 the tensor pipe's queue is what the issuers wait for in side-by-side steps, and issuing a
+  // step's two tiles in one burst (see `both` below) is slower there (24.1 vs 22.1 ms on the Wan-14B shape);
+  // at D = 64 the issuers' own instruction stream is the limit and the burst form wins (3.89 vs 4.17 ms).
+  constexpr bool FUSE_STEPS = (D == 64);
 #define PARO_STEP_GROUPS(e)                                                        \
   const int ka_ = (int)((e) & 0xFFFFu), kb_ = (int)((e) >> 16);                    \
   const bool shared_ = SHARE_TILES && ka_ == kb_;                                  \
@@ -266,6 +270,22 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
         const uint32_t a_kfull = smem_u32(bar_kfull);
         const uint64_t dK0 = smem_desc(smem_u32(sK), D);
         uint32_t st = 0, kph = 0;   // ring stage of the next tile and the parity of its current use
+        // the MMAs of one tile and their commit
+        auto issue = [&](auto wtag, const int i, const uint32_t stage) {
+          constexpr int W = decltype(wtag)::value;
+          const uint64_t dK = dK0 + (uint64_t)(stage * (uint32_t)(Cfg::K_BYTES >> 4));
+#pragma unroll
+          for (int k = 0; k < D / 32; ++k) {
+            if (W == 2) mma_i8_ts(tS, tQ + 8 * k, desc_advance(dK, 32 * k), IDESC_QK, k > 0);
+            else if (W == 0)   // lanes NOT written: the rows of the half the tile does not serve
+              mma_i8_ts_masked(tS, tQ + 8 * k, desc_advance(dK, 32 * k), IDESC_QK, k > 0, 0u, 0u, 0xffffffffu, 0xffffffffu);
+            else
+              mma_i8_ts_masked(tS, tQ + 8 * k, desc_advance(dK, 32 * k), IDESC_QK, k > 0, 0xffffffffu, 0xffffffffu, 0u, 0u);
+          }
+          // one commit per half served: the softmax warps wait on it for the scores, the K producer for the stage
+          if (W != 1) mma_commit_at(a_sready + 8u * (uint32_t)(i & 3));
+          if (W != 0) mma_commit_at(a_sready + 32u + 8u * (uint32_t)(i & 3));
+        };
         auto tile = [&](auto wtag, const int i, const int ev) -> bool {
           constexpr int W = decltype(wtag)::value;
           // the scores of step i-1 of the halves served are in registers: their rows of S may be
@@ -284,24 +304,34 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
           }
           TR(2, i, ev + 1);
           tc_fence_after();
-          const uint64_t dK = dK0 + (uint64_t)(st * (uint32_t)(Cfg::K_BYTES >> 4));
-#pragma unroll
-          for (int k = 0; k < D / 32; ++k) {
-            if (W == 2) mma_i8_ts(tS, tQ + 8 * k, desc_advance(dK, 32 * k), IDESC_QK, k > 0);
-            else if (W == 0)   // lanes NOT written: the rows of the half the tile does not serve
-              mma_i8_ts_masked(tS, tQ + 8 * k, desc_advance(dK, 32 * k), IDESC_QK, k > 0, 0u, 0u, 0xffffffffu, 0xffffffffu);
-            else
-              mma_i8_ts_masked(tS, tQ + 8 * k, desc_advance(dK, 32 * k), IDESC_QK, k > 0, 0xffffffffu, 0xffffffffu, 0u, 0u);
-          }
-          TR(2, i, ev + 2);
-          // one commit per half served: the softmax warps wait on it for the scores, the K producer for the stage
-          if (W != 1) mma_commit_at(a_sready + 8u * (uint32_t)(i & 3));
-          if (W != 0) mma_commit_at(a_sready + 32u + 8u * (uint32_t)(i & 3));
+          issue(wtag, i, st);
           if (++st == KST) {
             st = 0;
             kph ^= 1u;
           }
           TR(2, i, ev + 3);
+          return true;
+        };
+        // A side-by-side step (one tile per half) whose four barriers are all complete -- the usual case
+        // while this thread is what the walk waits for -- is issued as straight-line code: one branch for
+        // the step instead of one per poll, tile and ring wrap (a taken branch costs a lone thread
+        // about as much as issuing an MMA).
+        auto both = [&](const int i) -> bool {
+          const uint32_t par = (uint32_t)(i - 1) & 1u, ph = ((uint32_t)(i - 1) >> 1) & 1u;
+          const uint32_t wrap1 = st + 1 == KST ? 1u : 0u, st1 = wrap1 ? 0u : st + 1, ph1 = kph ^ wrap1;
+          TR(2, i, 0);
+          const bool r0 = mbar_poll(a_sfree + 8u * par, ph), r1 = mbar_poll(a_sfree + 16u + 8u * par, ph);
+          const bool r2 = mbar_poll(a_kfull + 8u * st, kph), r3 = mbar_poll(a_kfull + 8u * st1, ph1);
+          if (!(r0 & r1 & r2 & r3)) return false;
+          TR(2, i, 1);
+          tc_fence_after();
+          issue(std::integral_constant<int, 0>{}, i, st);
+          TR(2, i, 3);
+          issue(std::integral_constant<int, 1>{}, i, st1);
+          const uint32_t wrap2 = st1 + 1 == KST ? 1u : 0u;
+          st = wrap2 ? 0u : st1 + 1;
+          kph = ph1 ^ wrap2;
+          TR(2, i, 7);
           return true;
         };
         uint32_t e_cur = n_steps > 0 ? sched[0] : 0u, e_nxt = n_steps > 1 ? sched[1] : 0u;
@@ -313,6 +343,7 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
           if (SHARE_TILES && ka == kb && ka != 0xFFFFu) {
             good = tile(std::integral_constant<int, 2>{}, i, 0);
           } else {
+            if (FUSE_STEPS && ka != 0xFFFFu && kb != 0xFFFFu && both(i)) continue;
             good = ka == 0xFFFFu || tile(std::integral_constant<int, 0>{}, i, 0);
             good = good && (kb == 0xFFFFu || tile(std::integral_constant<int, 1>{}, i, 4));
           }
@@ -333,6 +364,24 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
       const uint32_t a_vfull = smem_u32(bar_vfull);
       const uint64_t dV0 = smem_desc(smem_u32(sV), 128);
       uint32_t st = 0, vph = 0;
+      auto issue = [&](auto wtag, const int i, const uint32_t stage) {
+        constexpr int W = decltype(wtag)::value;
+        const uint64_t dV = dV0 + (uint64_t)(stage * (uint32_t)(Cfg::V_BYTES >> 4));
+        // both halves start at step 0, so a tile that serves both never mixes a first with a later step
+        const uint32_t acc0 = i > 0 ? 1u : 0u;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const uint32_t acc = k > 0 ? 1u : acc0;
+          if (W == 2) mma_f16_ts(tO, tP + 8 * k, desc_advance(dV, 32 * k), IDESC_PV, acc);
+          else if (W == 0)
+            mma_f16_ts_masked(tO, tP + 8 * k, desc_advance(dV, 32 * k), IDESC_PV, acc, 0u, 0u, 0xffffffffu, 0xffffffffu);
+          else
+            mma_f16_ts_masked(tO, tP + 8 * k, desc_advance(dV, 32 * k), IDESC_PV, acc, 0xffffffffu, 0xffffffffu, 0u, 0u);
+        }
+        // one commit per half served: P of that half may be rewritten, and the V producer takes it for the stage
+        if (W != 1) mma_commit_at(a_pvdone + 8u * (uint32_t)(i & 3));
+        if (W != 0) mma_commit_at(a_pvdone + 32u + 8u * (uint32_t)(i & 3));
+      };
       auto tile = [&](auto wtag, const int i, const int ev) -> bool {
         constexpr int W = decltype(wtag)::value;
         const uint32_t par = (uint32_t)i & 1u, ph = ((uint32_t)i >> 1) & 1u;
@@ -349,26 +398,30 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
         }
         TR(3, i, ev + 1);
         tc_fence_after();
-        const uint64_t dV = dV0 + (uint64_t)(st * (uint32_t)(Cfg::V_BYTES >> 4));
-        // both halves start at step 0, so a tile that serves both never mixes a first with a later step
-        const uint32_t acc0 = i > 0 ? 1u : 0u;
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const uint32_t acc = k > 0 ? 1u : acc0;
-          if (W == 2) mma_f16_ts(tO, tP + 8 * k, desc_advance(dV, 32 * k), IDESC_PV, acc);
-          else if (W == 0)
-            mma_f16_ts_masked(tO, tP + 8 * k, desc_advance(dV, 32 * k), IDESC_PV, acc, 0u, 0u, 0xffffffffu, 0xffffffffu);
-          else
-            mma_f16_ts_masked(tO, tP + 8 * k, desc_advance(dV, 32 * k), IDESC_PV, acc, 0xffffffffu, 0xffffffffu, 0u, 0u);
-        }
-        TR(3, i, ev + 2);
-        if (W != 1) mma_commit_at(a_pvdone + 8u * (uint32_t)(i & 3));
-        if (W != 0) mma_commit_at(a_pvdone + 32u + 8u * (uint32_t)(i & 3));
+        issue(wtag, i, st);
         if (++st == VST) {
           st = 0;
           vph ^= 1u;
         }
         TR(3, i, ev + 3);
+        return true;
+      };
+      auto both = [&](const int i) -> bool {   // (as in the Q.K^T issuer)
+        const uint32_t par = (uint32_t)i & 1u, ph = ((uint32_t)i >> 1) & 1u;
+        const uint32_t wrap1 = st + 1 == VST ? 1u : 0u, st1 = wrap1 ? 0u : st + 1, ph1 = vph ^ wrap1;
+        TR(3, i, 0);
+        const bool r0 = mbar_poll(a_pready + 8u * par, ph), r1 = mbar_poll(a_pready + 16u + 8u * par, ph);
+        const bool r2 = mbar_poll(a_vfull + 8u * st, vph), r3 = mbar_poll(a_vfull + 8u * st1, ph1);
+        if (!(r0 & r1 & r2 & r3)) return false;
+        TR(3, i, 1);
+        tc_fence_after();
+        issue(std::integral_constant<int, 0>{}, i, st);
+        TR(3, i, 3);
+        issue(std::integral_constant<int, 1>{}, i, st1);
+        const uint32_t wrap2 = st1 + 1 == VST ? 1u : 0u;
+        st = wrap2 ? 0u : st1 + 1;
+        vph = ph1 ^ wrap2;
+        TR(3, i, 7);
         return true;
       };
       uint32_t e_cur = n_steps > 0 ? sched[0] : 0u, e_nxt = n_steps > 1 ? sched[1] : 0u;
@@ -380,6 +433,7 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
         if (SHARE_TILES && ka == kb && ka != 0xFFFFu) {
           good = tile(std::integral_constant<int, 2>{}, i, 0);
         } else {
+          if (FUSE_STEPS && ka != 0xFFFFu && kb != 0xFFFFu && both(i)) continue;
           good = ka == 0xFFFFu || tile(std::integral_constant<int, 0>{}, i, 0);
           good = good && (kb == 0xFFFFu || tile(std::integral_constant<int, 1>{}, i, 4));
         }
