@@ -881,7 +881,11 @@ extern "C" int paro_status_poll(const int32_t* status, int32_t* host_out, paro_s
 }
 
 #ifdef PARO_TRACE
+// Copies the trace table to the host and clears it on the device (synchronises).
 extern "C" int paro_debug_trace(long long* host_out) {
-  return cudaMemcpyFromSymbol(host_out, paro::g_trace, sizeof(paro::g_trace)) == cudaSuccess ? 0 : -1;
+  void* dev = nullptr;
+  if (cudaMemcpyFromSymbol(host_out, paro::g_trace, sizeof(paro::g_trace)) != cudaSuccess) return -1;
+  if (cudaGetSymbolAddress(&dev, paro::g_trace) != cudaSuccess) return -1;
+  return cudaMemset(dev, 0, sizeof(paro::g_trace)) == cudaSuccess ? 0 : -1;
 }
 #endif
