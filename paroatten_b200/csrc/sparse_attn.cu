@@ -124,7 +124,8 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
   static_assert(512 + 2 * D * 4 <= 1536 && 2048 + 2 * 128 * 4 <= Cfg::AUX_BYTES, "aux area too small");
   static_assert((27 + KST + VST) * 8 + 8 + 28 <= 512, "barrier area too small");
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // (the warp index through a shuffle: provably the same in all lanes, so the role branches are uniform)
+  const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
   // one thread decides for the whole CTA whether an earlier failure makes this launch drain (every
   // thread reading the word for itself could split the CTA around the collective operations below)
   if (threadIdx.x == 0) *s_drain = *reinterpret_cast<volatile int32_t*>(p.status) != 0;
@@ -253,7 +254,7 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
       }
       if (*abort_flag)
         for (int u = max(0, t - VST); u < t; ++u) mbar_wait_plain_bounded(bar_vfull + u % VST, (u / VST) & 1, WAIT_LIMIT);
-    } else if (warp == 10 && lane == 0) {
+    } else if (warp == 10) {
       // ---------------------------------------------------------------- MMA issuer: S = Q.K^T
       // (the two issuers are separate threads so that a P.V group waiting for room in the tensor
       // queue does not hold back the next scores, and vice versa)
@@ -263,9 +264,18 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
       // polls of a tile's barriers are issued together, ring position and phase are counters, and the
       // lane masks are compile-time constants of three instantiations of the tile code (W = 0 upper
       // half, 1 lower half, 2 both halves, unmasked form).
+      // The whole warp runs this loop converged (values below are made warp-uniform with a shuffle from
+      // lane 0, every decision is a vote), so that descriptors and addresses live in uniform registers;
+      // the tcgen05 instructions themselves are guarded by the elected lane's predicate.
       constexpr uint32_t IDESC_QK = instr_desc(2, 1, 1, 128, 64);  // s32 += s8 * s8
+      const uint32_t lead = elect_one();
+      const int n_steps_u = __shfl_sync(0xffffffffu, n_steps, 0);
+      const uint32_t tS_u = __shfl_sync(0xffffffffu, tS, 0), tQ_u = tS_u + 96u;
       do {
-        ATT_WAIT(bar_q, 0, 2, -1)
+        if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar_q, 0, abort_flag, WAIT_LIMIT))) {
+          report_timeout(p, abort_flag, 2, -1);
+          break;
+        }
         const uint32_t a_sfree = smem_u32(bar_sfree), a_sready = smem_u32(bar_sready);
         const uint32_t a_kfull = smem_u32(bar_kfull);
         const uint64_t dK0 = smem_desc(smem_u32(sK), D);
@@ -276,15 +286,15 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
           const uint64_t dK = dK0 + (uint64_t)(stage * (uint32_t)(Cfg::K_BYTES >> 4));
 #pragma unroll
           for (int k = 0; k < D / 32; ++k) {
-            if (W == 2) mma_i8_ts(tS, tQ + 8 * k, desc_advance(dK, 32 * k), IDESC_QK, k > 0);
+            if (W == 2) mma_i8_ts_p(lead, tS_u, tQ_u + 8 * k, desc_advance(dK, 32 * k), IDESC_QK, k > 0);
             else if (W == 0)   // lanes NOT written: the rows of the half the tile does not serve
-              mma_i8_ts_masked(tS, tQ + 8 * k, desc_advance(dK, 32 * k), IDESC_QK, k > 0, 0u, 0u, 0xffffffffu, 0xffffffffu);
+              mma_i8_ts_masked_p(lead, tS_u, tQ_u + 8 * k, desc_advance(dK, 32 * k), IDESC_QK, k > 0, 0u, 0u, 0xffffffffu, 0xffffffffu);
             else
-              mma_i8_ts_masked(tS, tQ + 8 * k, desc_advance(dK, 32 * k), IDESC_QK, k > 0, 0xffffffffu, 0xffffffffu, 0u, 0u);
+              mma_i8_ts_masked_p(lead, tS_u, tQ_u + 8 * k, desc_advance(dK, 32 * k), IDESC_QK, k > 0, 0xffffffffu, 0xffffffffu, 0u, 0u);
           }
           // one commit per half served: the softmax warps wait on it for the scores, the K producer for the stage
-          if (W != 1) mma_commit_at(a_sready + 8u * (uint32_t)(i & 3));
-          if (W != 0) mma_commit_at(a_sready + 32u + 8u * (uint32_t)(i & 3));
+          if (W != 1) mma_commit_at_p(lead, a_sready + 8u * (uint32_t)(i & 3));
+          if (W != 0) mma_commit_at_p(lead, a_sready + 32u + 8u * (uint32_t)(i & 3));
         };
         auto tile = [&](auto wtag, const int i, const int ev) -> bool {
           constexpr int W = decltype(wtag)::value;
@@ -295,12 +305,12 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
           const bool r0 = W == 1 || mbar_poll(a_sfree + 8u * par, ph);
           const bool r1 = W == 0 || mbar_poll(a_sfree + 16u + 8u * par, ph);
           const bool r2 = mbar_poll(a_kfull + 8u * st, kph);
-          if (!(r0 && r1 && r2)) {
+          if (!__all_sync(0xffffffffu, r0 && r1 && r2)) {
             bool good = true;
             if (W != 1) good = mbar_wait_bounded(bar_sfree + par, ph, abort_flag, WAIT_LIMIT);
             if (W != 0) good = good && mbar_wait_bounded(bar_sfree + 2 + par, ph, abort_flag, WAIT_LIMIT);
             good = good && mbar_wait_bounded(bar_kfull + st, kph, abort_flag, WAIT_LIMIT);
-            if (!good) return false;
+            if (!__all_sync(0xffffffffu, good)) return false;
           }
           TR(2, i, ev + 1);
           tc_fence_after();
@@ -322,7 +332,7 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
           TR(2, i, 0);
           const bool r0 = mbar_poll(a_sfree + 8u * par, ph), r1 = mbar_poll(a_sfree + 16u + 8u * par, ph);
           const bool r2 = mbar_poll(a_kfull + 8u * st, kph), r3 = mbar_poll(a_kfull + 8u * st1, ph1);
-          if (!(r0 & r1 & r2 & r3)) return false;
+          if (!__all_sync(0xffffffffu, r0 & r1 & r2 & r3)) return false;
           TR(2, i, 1);
           tc_fence_after();
           issue(std::integral_constant<int, 0>{}, i, st);
@@ -334,11 +344,12 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
           TR(2, i, 7);
           return true;
         };
-        uint32_t e_cur = n_steps > 0 ? sched[0] : 0u, e_nxt = n_steps > 1 ? sched[1] : 0u;
-        for (int i = 0; i < n_steps; ++i) {
-          const uint32_t ka = e_cur & 0xFFFFu, kb = e_cur >> 16;
+        uint32_t e_cur = n_steps_u > 0 ? sched[0] : 0u, e_nxt = n_steps_u > 1 ? sched[1] : 0u;
+        for (int i = 0; i < n_steps_u; ++i) {
+          const uint32_t e_u = __shfl_sync(0xffffffffu, e_cur, 0);
+          const uint32_t ka = e_u & 0xFFFFu, kb = e_u >> 16;
           e_cur = e_nxt;
-          if (i + 2 < n_steps) e_nxt = ld_pinned_u32(sched + i + 2);
+          if (i + 2 < n_steps_u) e_nxt = ld_pinned_u32(sched + i + 2);
           bool good;
           if (SHARE_TILES && ka == kb && ka != 0xFFFFu) {
             good = tile(std::integral_constant<int, 2>{}, i, 0);
@@ -354,12 +365,15 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
         }
       } while (false);
       if (*abort_flag) {   // the MMAs issued so far must retire before tensor memory is freed
-        mma_commit(bar_drain);
+        if (lead) mma_commit(bar_drain);
         mbar_wait_plain_bounded(bar_drain, 0, WAIT_LIMIT);
       }
-    } else if (warp == 11 && lane == 0) {
+    } else if (warp == 11) {
       // ---------------------------------------------------------------- MMA issuer: O += P.V
       constexpr uint32_t IDESC_PV = instr_desc(1, 1, 1, 128, D);   // f32 += bf16 * bf16
+      const uint32_t lead = elect_one();
+      const int n_steps_u = __shfl_sync(0xffffffffu, n_steps, 0);
+      const uint32_t tS_u = __shfl_sync(0xffffffffu, tS, 0), tP_u = tS_u + 64u, tO_u = tS_u + 128u;
       const uint32_t a_pready = smem_u32(bar_pready), a_pvdone = smem_u32(bar_pvdone);
       const uint32_t a_vfull = smem_u32(bar_vfull);
       const uint64_t dV0 = smem_desc(smem_u32(sV), 128);
@@ -372,15 +386,15 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
           const uint32_t acc = k > 0 ? 1u : acc0;
-          if (W == 2) mma_f16_ts(tO, tP + 8 * k, desc_advance(dV, 32 * k), IDESC_PV, acc);
+          if (W == 2) mma_f16_ts_p(lead, tO_u, tP_u + 8 * k, desc_advance(dV, 32 * k), IDESC_PV, acc);
           else if (W == 0)
-            mma_f16_ts_masked(tO, tP + 8 * k, desc_advance(dV, 32 * k), IDESC_PV, acc, 0u, 0u, 0xffffffffu, 0xffffffffu);
+            mma_f16_ts_masked_p(lead, tO_u, tP_u + 8 * k, desc_advance(dV, 32 * k), IDESC_PV, acc, 0u, 0u, 0xffffffffu, 0xffffffffu);
           else
-            mma_f16_ts_masked(tO, tP + 8 * k, desc_advance(dV, 32 * k), IDESC_PV, acc, 0xffffffffu, 0xffffffffu, 0u, 0u);
+            mma_f16_ts_masked_p(lead, tO_u, tP_u + 8 * k, desc_advance(dV, 32 * k), IDESC_PV, acc, 0xffffffffu, 0xffffffffu, 0u, 0u);
         }
         // one commit per half served: P of that half may be rewritten, and the V producer takes it for the stage
-        if (W != 1) mma_commit_at(a_pvdone + 8u * (uint32_t)(i & 3));
-        if (W != 0) mma_commit_at(a_pvdone + 32u + 8u * (uint32_t)(i & 3));
+        if (W != 1) mma_commit_at_p(lead, a_pvdone + 8u * (uint32_t)(i & 3));
+        if (W != 0) mma_commit_at_p(lead, a_pvdone + 32u + 8u * (uint32_t)(i & 3));
       };
       auto tile = [&](auto wtag, const int i, const int ev) -> bool {
         constexpr int W = decltype(wtag)::value;
@@ -389,12 +403,12 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
         const bool r0 = W == 1 || mbar_poll(a_pready + 8u * par, ph);
         const bool r1 = W == 0 || mbar_poll(a_pready + 16u + 8u * par, ph);
         const bool r2 = mbar_poll(a_vfull + 8u * st, vph);
-        if (!(r0 && r1 && r2)) {
+        if (!__all_sync(0xffffffffu, r0 && r1 && r2)) {
           bool good = true;
           if (W != 1) good = mbar_wait_bounded(bar_pready + par, ph, abort_flag, WAIT_LIMIT);
           if (W != 0) good = good && mbar_wait_bounded(bar_pready + 2 + par, ph, abort_flag, WAIT_LIMIT);
           good = good && mbar_wait_bounded(bar_vfull + st, vph, abort_flag, WAIT_LIMIT);
-          if (!good) return false;
+          if (!__all_sync(0xffffffffu, good)) return false;
         }
         TR(3, i, ev + 1);
         tc_fence_after();
@@ -412,7 +426,7 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
         TR(3, i, 0);
         const bool r0 = mbar_poll(a_pready + 8u * par, ph), r1 = mbar_poll(a_pready + 16u + 8u * par, ph);
         const bool r2 = mbar_poll(a_vfull + 8u * st, vph), r3 = mbar_poll(a_vfull + 8u * st1, ph1);
-        if (!(r0 & r1 & r2 & r3)) return false;
+        if (!__all_sync(0xffffffffu, r0 & r1 & r2 & r3)) return false;
         TR(3, i, 1);
         tc_fence_after();
         issue(std::integral_constant<int, 0>{}, i, st);
@@ -424,11 +438,12 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
         TR(3, i, 7);
         return true;
       };
-      uint32_t e_cur = n_steps > 0 ? sched[0] : 0u, e_nxt = n_steps > 1 ? sched[1] : 0u;
-      for (int i = 0; i < n_steps; ++i) {
-        const uint32_t ka = e_cur & 0xFFFFu, kb = e_cur >> 16;
+      uint32_t e_cur = n_steps_u > 0 ? sched[0] : 0u, e_nxt = n_steps_u > 1 ? sched[1] : 0u;
+      for (int i = 0; i < n_steps_u; ++i) {
+        const uint32_t e_u = __shfl_sync(0xffffffffu, e_cur, 0);
+        const uint32_t ka = e_u & 0xFFFFu, kb = e_u >> 16;
         e_cur = e_nxt;
-        if (i + 2 < n_steps) e_nxt = ld_pinned_u32(sched + i + 2);
+        if (i + 2 < n_steps_u) e_nxt = ld_pinned_u32(sched + i + 2);
         bool good;
         if (SHARE_TILES && ka == kb && ka != 0xFFFFu) {
           good = tile(std::integral_constant<int, 2>{}, i, 0);
@@ -443,7 +458,7 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
         }
       }
       if (*abort_flag) {
-        mma_commit(bar_drain + 1);
+        if (lead) mma_commit(bar_drain + 1);
         mbar_wait_plain_bounded(bar_drain + 1, 0, WAIT_LIMIT);
       }
     }

@@ -286,5 +286,71 @@ __device__ __forceinline__ void mma_commit_at(uint32_t bar_saddr) {
                : "memory");
 }
 
+// ----- forms for a role that runs with its whole warp converged -----------------------------------
+// All 32 lanes execute the role's loop, so everything the tcgen05 instructions take (descriptors, TMEM
+// addresses, barrier addresses) is warp-uniform and can be formed in uniform registers; only the
+// instruction itself is guarded by the elected lane's predicate (`lead` != 0 in exactly one lane).
+__device__ __forceinline__ uint32_t elect_one() {
+  uint32_t lead;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(lead));
+  return lead;
+}
+__device__ __forceinline__ void mma_i8_ts_p(uint32_t lead, uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
+                                            uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "setp.ne.b32 q, %5, 0;\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::i8 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(lead)
+      : "memory");
+}
+__device__ __forceinline__ void mma_i8_ts_masked_p(uint32_t lead, uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
+                                                   uint32_t idesc, uint32_t accumulate, uint32_t m0, uint32_t m1,
+                                                   uint32_t m2, uint32_t m3) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "setp.ne.b32 q, %9, 0;\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::i8 [%0], [%1], %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(m0), "r"(m1), "r"(m2), "r"(m3),
+        "r"(lead)
+      : "memory");
+}
+__device__ __forceinline__ void mma_f16_ts_p(uint32_t lead, uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
+                                             uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "setp.ne.b32 q, %5, 0;\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(lead)
+      : "memory");
+}
+__device__ __forceinline__ void mma_f16_ts_masked_p(uint32_t lead, uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
+                                                    uint32_t idesc, uint32_t accumulate, uint32_t m0, uint32_t m1,
+                                                    uint32_t m2, uint32_t m3) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "setp.ne.b32 q, %9, 0;\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(m0), "r"(m1), "r"(m2), "r"(m3),
+        "r"(lead)
+      : "memory");
+}
+__device__ __forceinline__ void mma_commit_at_p(uint32_t lead, uint32_t bar_saddr) {
+  asm volatile(
+      "{\n\t.reg .pred q;\n\t"
+      "setp.ne.b32 q, %1, 0;\n\t"
+      "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}"
+      ::"r"(bar_saddr), "r"(lead)
+      : "memory");
+}
+
 }  // namespace umma
 }  // namespace paro
