@@ -143,13 +143,13 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
   const int n_steps = max(n_a, n_b);
   // A step has one MMA group of each kind per tile: group 0 serves the upper half, or both halves
   // when the tile is shared (kbA == kbB); group 1 serves the lower half.  Sharing halves the tensor
-  // work of such a step but makes the two halves wait for each other in it; at D = 64 the tensor pipe
-  // is not what limits the kernel and the wait costs 13 % on the CogVideoX shape, so tiles are only
-  // shared at D = 128.
-  constexpr bool SHARE_TILES = (D == 128);
-  // At D = 128 the tensor pipe's queue is what the issuers wait for in side-by-side steps, and issuing a
-  // step's two tiles in one burst (see `both` below) is slower there (24.1 vs 22.1 ms on the Wan-14B shape);
-  // at D = 64 the issuers' own instruction stream is the limit and the burst form wins (3.89 vs 4.17 ms).
+  // work of such a step but makes the two halves wait for each other in it.  (With single-lane
+  // issuers that wait cost more than it saved at D = 64; with the issuers running warp-wide sharing
+  // wins there too: 3.85 vs 3.96 ms on the CogVideoX shape.)
+  constexpr bool SHARE_TILES = true;
+  // Issuing a side-by-side step's two tiles in one burst (see `both` below) is slower at D = 128, where the
+  // tensor pipe is what the issuers wait for (21.5 vs 21.1 ms on the Wan-14B shape), and a little faster at
+  // D = 64.
   constexpr bool FUSE_STEPS = (D == 64);
 #define PARO_STEP_GROUPS(e)                                                        \
   const int ka_ = (int)((e) & 0xFFFFu), kb_ = (int)((e) >> 16);                    \
