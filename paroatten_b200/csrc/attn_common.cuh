@@ -133,23 +133,4 @@ __device__ __forceinline__ uint32_t commit_token(uint32_t bars_saddr, int half, 
   return (bars_saddr + 32u * (uint32_t)half + 8u * ((uint32_t)step & 3u)) | ((((uint32_t)step >> 2) & 1u) << 31);
 }
 
-// One schedule entry = kbA | kbB << 16 (0xFFFF: no tile for that half in this step).  A step has one
-// MMA group of each kind per tile: group 0 serves the upper half, or both halves when the tile is
-// shared (kbA == kbB and SHARE); group 1 serves the lower half.
-struct StepGroups {
-  bool act[2];
-  int kblk[2];
-  int which[2];   // 0 upper half, 1 lower half, 2 both
-  __device__ __forceinline__ StepGroups(uint32_t e, bool share) {
-    const int ka = (int)(e & 0xFFFFu), kb = (int)(e >> 16);
-    const bool shared = share && ka == kb;
-    act[0] = ka != 0xFFFF;
-    act[1] = !shared && kb != 0xFFFF;
-    kblk[0] = ka;
-    kblk[1] = kb;
-    which[0] = shared ? 2 : 0;
-    which[1] = 1;
-  }
-};
-
 }  // namespace paro

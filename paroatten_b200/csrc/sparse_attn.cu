@@ -15,23 +15,30 @@
 //               warp w (< 4, set 0) handles the even steps of its half, warp w+4 (set 1) the odd
 //               steps (both may touch TMEM lane quadrant w).  A thread handles the whole row (64
 //               scores) of its steps, so two consecutive steps of a half are in flight at once.
-//               Online softmax in fp32 (base 2, lazy rescaling): the running row maximum passes
-//               from step to step through shared memory, each thread keeps its own share of the
-//               row sum.  P is written to TMEM as bf16; the epilogue stores O/l * v_scale + vm at
-//               the row's un-permuted position.  These warps take the registers the others give up.
-//   warp 8      TMA producer for the K ring (int8 tiles, freed when their Q.K^T is done)
-//   warp 9      TMA producer for the V^T ring (bf16 tiles, freed when their P.V is done)
-//   warp 10     owns TMEM; one lane issues S = Q.K^T (kind::i8, A = Q from TMEM, int32 accumulators)
-//   warp 11     one lane issues O += P.V (kind::f16, A = P from TMEM, fp32 accumulators in TMEM)
+//               Base-2 softmax in fp32; each thread keeps its own share of the row sum (and, in the
+//               exact walk, the running row maximum passes from step to step through shared memory).
+//               P is written to TMEM as bf16; the epilogue stores O/l * v_scale + vm at the row's
+//               un-permuted position.  These warps take the registers the others give up.
+//   warp 8      one lane: TMA producer for the K ring (int8 tiles)
+//   warp 9      one lane: TMA producer for the V^T ring (bf16 tiles)
+//   warp 10     owns TMEM; issues S = Q.K^T (kind::i8, A = Q from TMEM, int32 accumulators)
+//   warp 11     issues O += P.V (kind::f16 on bf16, A = P from TMEM, fp32 accumulators in TMEM)
+//               The two issuer warps run their loops with all 32 lanes converged, so that descriptors
+//               and addresses are formed in uniform registers; the tcgen05 instructions themselves
+//               are guarded by the elected lane's predicate.
+//
+// Hand-offs.  An issuer commits ONCE per tile, to the barrier of (half, step mod 4): "scores ready"
+// for Q.K^T, "P.V done" for P.V.  The softmax warps wait on it, and so does the ring's producer when it
+// wants that tile's stage back.  The softmax warps release S the moment the scores are in registers
+// and write P after all of a step's arithmetic.
 //
 // TMEM (256 columns per CTA): S [0,64) int32 scores, P [64,96) bf16 probabilities, Q [96,128) the
 // int8 query tile (A operand of Q.K^T read from TMEM, so it is not re-read from shared memory for
-// every k-block), O [128,128+D) fp32.  The softmax threads release S as soon as they hold the scores
-// in registers, so Q.K^T of step i+1 overlaps the exponentials of step i (and the other warp set
-// starts on step i+1 while step i is still being exponentiated), and P.V of step i overlaps the
-// softmax of step i+1; two CTAs share an SM so that one CTA's softmax overlaps the other's MMAs.
-// Every wait is bounded: on expiry the CTA records a code in the status words, raises a shared
-// abort flag and unwinds (TMEM freed).
+// every k-block), O [128,128+D) fp32.  Q.K^T of step i+1 overlaps the exponentials of step i (and the
+// other warp set starts on step i+1 while step i is still being exponentiated), and P.V of step i
+// overlaps the softmax of step i+1; two CTAs share an SM so that one CTA's softmax overlaps the
+// other's MMAs.  Every wait is bounded: on expiry the CTA records a code in the status words, raises
+// a shared abort flag and unwinds (copies landed, MMAs retired, TMEM freed).
 #include <mutex>
 #include <type_traits>
 
@@ -256,14 +263,13 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
         for (int u = max(0, t - VST); u < t; ++u) mbar_wait_plain_bounded(bar_vfull + u % VST, (u / VST) & 1, WAIT_LIMIT);
     } else if (warp == 10) {
       // ---------------------------------------------------------------- MMA issuer: S = Q.K^T
-      // (the two issuers are separate threads so that a P.V group waiting for room in the tensor
+      // (the two issuers are separate warps so that a P.V group waiting for room in the tensor
       // queue does not hold back the next scores, and vice versa)
-      // Each issuer is one thread running dependent scalar code next to the softmax warps, and every
-      // tile of the walk passes through it, so its instruction count per tile is on the kernel's
-      // critical path.  Hence: barrier addresses and the stage-0 descriptor are formed once, the
-      // polls of a tile's barriers are issued together, ring position and phase are counters, and the
-      // lane masks are compile-time constants of three instantiations of the tile code (W = 0 upper
-      // half, 1 lower half, 2 both halves, unmasked form).
+      // Every tile of the walk passes through an issuer, so its instruction count per tile is on the
+      // kernel's critical path.  Hence: barrier addresses and the stage-0 descriptor are formed once,
+      // the polls of a tile's barriers are issued together, ring position and phase are counters, and
+      // the lane masks are compile-time constants of three instantiations of the tile code (W = 0
+      // upper half, 1 lower half, 2 both halves, unmasked form).
       // The whole warp runs this loop converged (values below are made warp-uniform with a shuffle from
       // lane 0, every decision is a vote), so that descriptors and addresses live in uniform registers;
       // the tcgen05 instructions themselves are guarded by the elected lane's predicate.
