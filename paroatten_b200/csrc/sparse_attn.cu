@@ -55,8 +55,10 @@ using namespace umma;
 #ifdef PARO_TRACE
 __device__ long long g_trace[16][160][8];
 #define TR(role, step, ev) do { if (FIXED && blockIdx.x == PARO_TRACE && (step) < 160) g_trace[role][step][ev] = clock64(); } while (0)
+#define TRL(role, step, ev) do { if (lead) TR(role, step, ev); } while (0)   // in a role whose whole warp runs: one lane stamps
 #else
 #define TR(role, step, ev)
+#define TRL(role, step, ev)
 #endif
 constexpr float RESCALE_TAU = 8.0f;            // exact walk: rescale O only when the row max grows by > 2^8
 constexpr float REF_OFFSET = 20.f;             // fixed reference: the first block's maximum maps to P = 2^-20
@@ -307,7 +309,7 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
           // the scores of step i-1 of the halves served are in registers: their rows of S may be
           // overwritten.  (i = 0 asks an unused barrier for parity 1, which passes at once.)
           const uint32_t par = (uint32_t)(i - 1) & 1u, ph = ((uint32_t)(i - 1) >> 1) & 1u;
-          TR(2, i, ev + 0);
+          TRL(2, i, ev + 0);
           const bool r0 = W == 1 || mbar_poll(a_sfree + 8u * par, ph);
           const bool r1 = W == 0 || mbar_poll(a_sfree + 16u + 8u * par, ph);
           const bool r2 = mbar_poll(a_kfull + 8u * st, kph);
@@ -318,14 +320,14 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
             good = good && mbar_wait_bounded(bar_kfull + st, kph, abort_flag, WAIT_LIMIT);
             if (!__all_sync(0xffffffffu, good)) return false;
           }
-          TR(2, i, ev + 1);
+          TRL(2, i, ev + 1);
           tc_fence_after();
           issue(wtag, i, st);
           if (++st == KST) {
             st = 0;
             kph ^= 1u;
           }
-          TR(2, i, ev + 3);
+          TRL(2, i, ev + 3);
           return true;
         };
         // A side-by-side step (one tile per half) whose four barriers are all complete -- the usual case
@@ -335,19 +337,19 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
         auto both = [&](const int i) -> bool {
           const uint32_t par = (uint32_t)(i - 1) & 1u, ph = ((uint32_t)(i - 1) >> 1) & 1u;
           const uint32_t wrap1 = st + 1 == KST ? 1u : 0u, st1 = wrap1 ? 0u : st + 1, ph1 = kph ^ wrap1;
-          TR(2, i, 0);
+          TRL(2, i, 0);
           const bool r0 = mbar_poll(a_sfree + 8u * par, ph), r1 = mbar_poll(a_sfree + 16u + 8u * par, ph);
           const bool r2 = mbar_poll(a_kfull + 8u * st, kph), r3 = mbar_poll(a_kfull + 8u * st1, ph1);
           if (!__all_sync(0xffffffffu, r0 & r1 & r2 & r3)) return false;
-          TR(2, i, 1);
+          TRL(2, i, 1);
           tc_fence_after();
           issue(std::integral_constant<int, 0>{}, i, st);
-          TR(2, i, 3);
+          TRL(2, i, 3);
           issue(std::integral_constant<int, 1>{}, i, st1);
           const uint32_t wrap2 = st1 + 1 == KST ? 1u : 0u;
           st = wrap2 ? 0u : st1 + 1;
           kph = ph1 ^ wrap2;
-          TR(2, i, 7);
+          TRL(2, i, 7);
           return true;
         };
         uint32_t e_cur = n_steps_u > 0 ? sched[0] : 0u, e_nxt = n_steps_u > 1 ? sched[1] : 0u;
@@ -405,7 +407,7 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
       auto tile = [&](auto wtag, const int i, const int ev) -> bool {
         constexpr int W = decltype(wtag)::value;
         const uint32_t par = (uint32_t)i & 1u, ph = ((uint32_t)i >> 1) & 1u;
-        TR(3, i, ev + 0);
+        TRL(3, i, ev + 0);
         const bool r0 = W == 1 || mbar_poll(a_pready + 8u * par, ph);
         const bool r1 = W == 0 || mbar_poll(a_pready + 16u + 8u * par, ph);
         const bool r2 = mbar_poll(a_vfull + 8u * st, vph);
@@ -416,32 +418,32 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
           good = good && mbar_wait_bounded(bar_vfull + st, vph, abort_flag, WAIT_LIMIT);
           if (!__all_sync(0xffffffffu, good)) return false;
         }
-        TR(3, i, ev + 1);
+        TRL(3, i, ev + 1);
         tc_fence_after();
         issue(wtag, i, st);
         if (++st == VST) {
           st = 0;
           vph ^= 1u;
         }
-        TR(3, i, ev + 3);
+        TRL(3, i, ev + 3);
         return true;
       };
       auto both = [&](const int i) -> bool {   // (as in the Q.K^T issuer)
         const uint32_t par = (uint32_t)i & 1u, ph = ((uint32_t)i >> 1) & 1u;
         const uint32_t wrap1 = st + 1 == VST ? 1u : 0u, st1 = wrap1 ? 0u : st + 1, ph1 = vph ^ wrap1;
-        TR(3, i, 0);
+        TRL(3, i, 0);
         const bool r0 = mbar_poll(a_pready + 8u * par, ph), r1 = mbar_poll(a_pready + 16u + 8u * par, ph);
         const bool r2 = mbar_poll(a_vfull + 8u * st, vph), r3 = mbar_poll(a_vfull + 8u * st1, ph1);
         if (!__all_sync(0xffffffffu, r0 & r1 & r2 & r3)) return false;
-        TR(3, i, 1);
+        TRL(3, i, 1);
         tc_fence_after();
         issue(std::integral_constant<int, 0>{}, i, st);
-        TR(3, i, 3);
+        TRL(3, i, 3);
         issue(std::integral_constant<int, 1>{}, i, st1);
         const uint32_t wrap2 = st1 + 1 == VST ? 1u : 0u;
         st = wrap2 ? 0u : st1 + 1;
         vph = ph1 ^ wrap2;
-        TR(3, i, 7);
+        TRL(3, i, 7);
         return true;
       };
       uint32_t e_cur = n_steps_u > 0 ? sched[0] : 0u, e_nxt = n_steps_u > 1 ? sched[1] : 0u;
