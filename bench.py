@@ -199,7 +199,7 @@ class Workload:
         if not permute:
             self.orders_all.zero_()
         self.mask_all = make_mask(H, nb, wl["density"], 0, (self.n_text + 63) // 64, wl["window"])
-        self.plan = pb.compact_plan(self.mask_all[self.h0:self.h1].to(dev))
+        self.plan = pb.compact_plan(self.mask_all[self.h0:self.h1].to(dev), pairing="overlap")
         self.pplan = pb.PermutePlan({"permute": self.orders_all[self.h0:self.h1].to(dev).reshape(1, -1)}, wl["grid"], dev)
         self.rope = pb.rope_tables(wl["grid"], D, wl["family"], device=dev)
         self.kept_local = self.plan.kept_blocks * B

@@ -195,7 +195,11 @@ int paro_plan_fill(const uint8_t* mask, int slices, int nbq, int nbk,
  * block only 2p+1 keeps.  sched [size of pair_ent], entries of pair r from offset pair_ptr[r]:
  * kbA | kbB << 16, 0xFFFF = no tile for that q-block in this step (needs nbk < 65535);
  * sched_cnt [2 * slices*ceil(nbq/2)]: steps of q-block 2p, steps of q-block 2p+1 (each contiguous
- * from step 0).  No counterpart in the reference (it tests one mask byte per block in the loop,
+ * from step 0), in the low 16 bits of each word.  A caller that pairs q-blocks differently (the walk
+ * costs the UNION of a pair's two lists, so q-blocks that share many k-blocks make cheap pairs) builds
+ * the lists from the mask with its rows in pair order and, before handing sched_cnt to paro_sparse_attn,
+ * ORs (q-block id + 1) << 16 into each word: the half then stands for that q-block (rows, scales, output
+ * rows); high half 0 = the adjacent pairing.  No counterpart in the reference (it tests one mask byte per block in the loop,
  * qk_int_sv_f16_cuda_sm80.cu:268). */
 int paro_plan_schedule(const int32_t* pair_ptr, const int32_t* pair_ent, int slices, int nbq, int nbk,
                        uint32_t* sched, int32_t* sched_cnt, paro_stream_t stream);

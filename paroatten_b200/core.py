@@ -142,7 +142,7 @@ def sparse_attn_quantized(q_int8, q_scale, k_int8, k_scale, v16, v_scale, vm, pl
         _lib.check(_lib.lib().paro_sparse_attn(
             q_int8.data_ptr(), k_int8.data_ptr(), v16.data_ptr(), q_scale.data_ptr(), int(q_group),
             k_scale.data_ptr(), v_scale.data_ptr(), _lib.ptr(vm), plan.pair_ptr.data_ptr(), plan.sched.data_ptr(),
-            plan.sched_cnt.data_ptr(),
+            (plan.sched_cnt_kernel if plan.sched_cnt_kernel is not None else plan.sched_cnt).data_ptr(),
             plan.slices, _lib.ptr(inv_index), int(n_text), out.data_ptr(), _lib.dtype_code(out.dtype),
             ov.stride(0), ov.stride(1), ov.stride(2), _lib.ptr(lse), B, H, N, D, float(sm_scale),
             _lib.ATTN_FAST if mode == "fast" else _lib.ATTN_EXACT, _lib.ptr(redo),
@@ -317,9 +317,10 @@ def paro_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, permute_pl
         elif isinstance(sparse_plan, CompactPlan):
             plan = sparse_plan
         elif sparse_plan.dim() == 5:
-            plan = compact_plan(apply_empty_heads(sparse_plan[i_timestep, i_block].to(dev), empty, n_text_blocks))
+            plan = compact_plan(apply_empty_heads(sparse_plan[i_timestep, i_block].to(dev), empty, n_text_blocks),
+                                pairing="overlap")
         else:
-            plan = compact_plan(apply_empty_heads(sparse_plan.to(dev), empty, n_text_blocks))
+            plan = compact_plan(apply_empty_heads(sparse_plan.to(dev), empty, n_text_blocks), pairing="overlap")
         # Q and V: the quantisers read the natural-order tensors through the RoPE + reordering front end
         # (no reordered 16-bit copy).  Smoothed K needs the mean of the rotated values first; rotating
         # twice costs more than writing the rotated copy once, so K keeps the two-step form.

@@ -38,8 +38,13 @@ __global__ void plan_validate_kernel(const int32_t* __restrict__ pair_ptr, const
       continue;
     }
     const int slots = (int)(e1 - e0);
-    const int na = cnt[2 * r], nb = cnt[2 * r + 1];
+    const int na = cnt[2 * r] & 0xFFFF, nb = cnt[2 * r + 1] & 0xFFFF;   // (high halves: optional q-block ids)
     const bool has_second = 2 * (r % npairs) + 1 < nbq;
+    const int qa = (int)((uint32_t)cnt[2 * r] >> 16), qb = (int)((uint32_t)cnt[2 * r + 1] >> 16);
+    if (qa > nbq || qb > nbq) {   // q-block id + 1 of a half, 0 = none given
+      if (lane == 0) fault(PLAN_BAD_BLOCK, r, -1, qa > nbq ? qa - 1 : qb - 1);
+      continue;
+    }
     if (na < 0 || nb < 0 || na > slots || nb > slots || (!has_second && nb != 0)) {
       if (lane == 0) fault(PLAN_BAD_COUNT, r, 0, na > slots || na < 0 ? na : nb);
       continue;

@@ -148,7 +148,10 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
   // halves' remaining blocks side by side; each half's steps are contiguous from step 0.
   const int prow = slice * p.npairs + pair;
   const uint32_t* sched = p.sched + p.pair_ptr[prow];
-  const int n_a = p.sched_cnt[2 * prow], n_b = p.sched_cnt[2 * prow + 1];
+  // per half: steps in the low 16 bits; the high 16 bits are 0 (the pair is q-blocks 2p and 2p+1) or hold
+  // 1 + the q-block the half stands for, when the plan paired q-blocks by the k-blocks they share
+  const uint32_t cnt_a = (uint32_t)p.sched_cnt[2 * prow], cnt_b = (uint32_t)p.sched_cnt[2 * prow + 1];
+  const int n_a = (int)(cnt_a & 0xFFFFu), n_b = (int)(cnt_b & 0xFFFFu);
   const int n_steps = max(n_a, n_b);
   // A step has one MMA group of each kind per tile: group 0 serves the upper half, or both halves
   // when the tile is shared (kbA == kbB); group 1 serves the lower half.  Sharing halves the tensor
@@ -486,7 +489,9 @@ sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
     }
     named_barrier(1, ATT_SOFTMAX_THREADS);
 
-    const int tok = pair * 128 + r;
+    const uint32_t cnt_mine = half ? cnt_b : cnt_a;
+    const int qblk = (cnt_mine >> 16) ? (int)(cnt_mine >> 16) - 1 : 2 * pair + half;
+    const int tok = qblk * 64 + (r & 63);
     if (set == 0) {
       // this thread's query row goes to TMEM (four int8 per 32-bit column); rows past the end are zero
       uint32_t qrow[D / 4];

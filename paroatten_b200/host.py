@@ -106,7 +106,7 @@ class HostPipelinedAttention:
         self.groups: List[Tuple[int, int]] = head_groups(H, heads_per_group)
         g = max(h1 - h0 for h0, h1 in self.groups)
         with torch.cuda.device(self.device):
-            self.plans: List[CompactPlan] = [compact_plan(mask[h0:h1].to(self.device)) for h0, h1 in self.groups]
+            self.plans: List[CompactPlan] = [compact_plan(mask[h0:h1].to(self.device), pairing="overlap") for h0, h1 in self.groups]
             self.pplans = [PermutePlan({"permute": orders[h0:h1].reshape(1, -1)}, self.kw["grid_fhw"], self.device)
                            for h0, h1 in self.groups]
             # two sets of staging buffers: one being filled while the other is consumed

@@ -45,18 +45,22 @@ class CompactPlan:
     kept_blocks: int         # number of true entries of the mask
     pair_tiles: int          # size of the merged (union) lists over all q-block pairs
     sched: Optional[torch.Tensor] = None       # int32 [pair_tiles]: kbA | kbB << 16 per step (what the kernel walks)
-    sched_cnt: Optional[torch.Tensor] = None   # int32 [slices*ceil(nbq/2), 2]: steps of q-block 2p and of 2p+1
+    sched_cnt: Optional[torch.Tensor] = None   # int32 [slices*ceil(nbq/2), 2]: steps of the pair's two q-blocks
+    # pairing="overlap": the q-blocks each pair is made of, int32 [slices*ceil(nbq/2), 2] (-1: none); row_ptr/cols,
+    # pair_ent and sched are then those of the mask with its rows in that order.  None: pair p = q-blocks 2p, 2p+1.
+    pair_q: Optional[torch.Tensor] = None
+    sched_cnt_kernel: Optional[torch.Tensor] = None   # what the kernel reads: sched_cnt | (pair_q + 1) << 16
 
     @property
     def steps(self) -> int:
         """Steps of the kernel's walk over all pairs (a step is one or two MMA groups)."""
-        return int(self.sched_cnt.max(dim=1).values.sum().item())
+        return int((self.sched_cnt & 0xFFFF).max(dim=1).values.sum().item())
 
     @property
     def tiles(self) -> int:
         """K/V tiles the kernel loads = MMA groups of each kind it issues: a tile shared by both
         q-blocks of a pair counts once."""
-        c = self.sched_cnt.long()
+        c = (self.sched_cnt & 0xFFFF).long()
         n = int(c.sum().item())
         return n - self.shared_tiles
 
@@ -98,10 +102,57 @@ def validate_plan(plan: "CompactPlan") -> None:
             plan.sched.numel(), report.data_ptr(), _lib.stream_ptr()))
 
 
-def compact_plan(mask: torch.Tensor, validate: Optional[bool] = None) -> CompactPlan:
+def pair_rows_by_overlap(m: torch.Tensor) -> torch.Tensor:
+    """m: uint8/bool [slices, nbq, nbk] on the GPU.  Returns int64 [slices, nbq]: an order of the q-blocks
+    in which rows 2p and 2p+1 are good partners -- the kernel walks the UNION of a pair's two lists, a
+    k-block both keep costs one tile instead of two.  Greedy: the first q-block not yet paired takes the
+    free q-block it shares most k-blocks with (ties: the lowest index).  Deterministic; nbq/2 rounds of a
+    few small kernels, vectorised over the slices."""
+    S, nbq, _ = m.shape
+    mf = m.to(torch.float32)
+    ov = torch.bmm(mf, mf.transpose(1, 2))                    # shared k-blocks of every two q-blocks
+    idx = torch.arange(S, device=m.device)
+    free = torch.ones(S, nbq, dtype=torch.bool, device=m.device)
+    order = torch.empty(S, nbq, dtype=torch.int64, device=m.device)
+    for pidx in range(nbq // 2):
+        i = free.to(torch.uint8).argmax(dim=1)                # first free row of each slice
+        free[idx, i] = False
+        cand = torch.where(free, ov[idx, i], torch.full_like(ov[idx, i], -1.0))
+        j = cand.argmax(dim=1)
+        free[idx, j] = False
+        order[:, 2 * pidx] = i
+        order[:, 2 * pidx + 1] = j
+    if nbq % 2:
+        order[:, nbq - 1] = free.to(torch.uint8).argmax(dim=1)
+    return order
+
+
+def compact_plan(mask: torch.Tensor, validate: Optional[bool] = None, pairing: str = "adjacent") -> CompactPlan:
     """mask: bool/uint8 [..., nbq, nbk] on the GPU (leading dims are flattened to slices).
     validate: run validate_plan on the result (default: only when the environment variable
-    PARO_DEBUG_PLANS is set to a non-empty value other than 0)."""
+    PARO_DEBUG_PLANS is set to a non-empty value other than 0).
+    pairing: "adjacent" -- work item p is q-blocks 2p and 2p+1; "overlap" -- q-blocks are paired by the
+    k-blocks they share (pair_rows_by_overlap), kept only if that needs fewer tiles than adjacency."""
+    if pairing not in ("adjacent", "overlap"):
+        raise ValueError(f"unknown pairing {pairing!r}")
+    if pairing == "overlap":
+        _lib.require_cuda(mask)
+        nbq0, nbk0 = int(mask.shape[-2]), int(mask.shape[-1])
+        m0 = mask.reshape(-1, nbq0, nbk0)
+        m0 = (m0 if m0.dtype in (torch.uint8, torch.bool) else (m0 != 0)).contiguous().view(torch.uint8)
+        base = compact_plan(m0, validate=validate)
+        if nbq0 < 4 or nbq0 >= 0xFFFF:
+            return base
+        order = pair_rows_by_overlap(m0)
+        plan = compact_plan(torch.gather(m0, 1, order.unsqueeze(-1).expand(-1, -1, nbk0)), validate=validate)
+        if plan.pair_tiles >= base.pair_tiles:
+            return base
+        npairs0 = (nbq0 + 1) // 2
+        pq = torch.full((m0.shape[0], 2 * npairs0), -1, dtype=torch.int32, device=m0.device)
+        pq[:, :nbq0] = order.to(torch.int32)
+        plan.pair_q = pq.view(-1, 2).contiguous()
+        plan.sched_cnt_kernel = (plan.sched_cnt | ((plan.pair_q + 1) << 16)).contiguous()
+        return plan
     _lib.require_cuda(mask)
     if validate is None:
         import os
@@ -151,7 +202,8 @@ class SparsePlan:
     def get(self, i_timestep: int, i_block: int) -> CompactPlan:
         key = (int(i_timestep), int(i_block))
         if key not in self._cache:
-            self._cache[key] = compact_plan(self.sparse[key[0], key[1]].to(self.device, non_blocking=True))
+            self._cache[key] = compact_plan(self.sparse[key[0], key[1]].to(self.device, non_blocking=True),
+                                            pairing="overlap")
         return self._cache[key]
 
 
@@ -211,8 +263,12 @@ class PlanStore:
             for t in range(T):
                 for l in range(L):
                     p = compact_plan(apply_empty_heads(sparse[t, l].to(self.device),
-                                                       None if empty is None else empty[l], n_text_blocks))
-                    self.lists[(t, l)] = tuple(x.cpu().pin_memory() for x in (p.pair_ptr, p.sched, p.sched_cnt))
+                                                       None if empty is None else empty[l], n_text_blocks),
+                                     pairing="overlap")
+                    # (the step counts are stored in the form the kernel reads: with the pairs' q-block ids
+                    # in their high halves when the q-blocks were paired by overlap)
+                    cnt = p.sched_cnt_kernel if p.sched_cnt_kernel is not None else p.sched_cnt
+                    self.lists[(t, l)] = tuple(x.cpu().pin_memory() for x in (p.pair_ptr, p.sched, cnt))
                     self.kept[(t, l)] = p.kept_blocks
         cap = max(c.numel() for _, c, _ in self.lists.values())
         prows = self.meta["H"] * ((self.meta["nbq"] + 1) // 2)

@@ -40,8 +40,8 @@ def quantised(q, k, v, orders, grid, n_text=0):
     (64, 976, 2, 0.3, torch.bfloat16),      # tail 16, odd block count (pair with a missing half)
     (128, 4160, 2, 0.2, torch.bfloat16),    # 65 blocks: long lists, ring wrap-around
 ])
-@pytest.mark.parametrize("mode", ["fast", "exact"])
-def test_kernel_on_oracle_quantised_operands(D, N, H, density, dtype, mode):
+@pytest.mark.parametrize("mode,pairing", [("fast", "adjacent"), ("exact", "adjacent"), ("fast", "overlap")])
+def test_kernel_on_oracle_quantised_operands(D, N, H, density, dtype, mode, pairing):
     """The kernel alone: operands quantised by the ORACLE, so only the attention differs.  Both
     walks: the fast one (fixed reference exponent per row) and the exact one (running maximum)."""
     B = 2
@@ -50,7 +50,7 @@ def test_kernel_on_oracle_quantised_operands(D, N, H, density, dtype, mode):
     mask = po.make_mask(H, nb, density, seed=N)
     q8, qs, k8, ks, v8, vs, vm = quantised(q, k, v, [0] * H, (1, 1, N))
     want, want_lse = po.sparse_attention(q8, qs, k8, ks, v8, vs, vm, mask, D ** -0.5, out_dtype=dtype, return_lse=True)
-    plan = pb.compact_plan(mask.to(DEV))
+    plan = pb.compact_plan(mask.to(DEV), pairing=pairing)   # "overlap": q-blocks paired by the k-blocks they share
     got, lse = pb.sparse_attn_quantized(q8.to(DEV), qs.to(DEV), k8.to(DEV), ks.to(DEV), v8.to(torch.bfloat16).to(DEV),
                                         vs.to(DEV), vm.to(DEV), plan, D ** -0.5, out_dtype=dtype, return_lse=True,
                                         mode=mode)
@@ -351,8 +351,17 @@ def test_plan_store_prefetch_and_roundtrip(tmp_path):
             for l in range(L):
                 st.prefetch(t, l + 1)
                 plan = st.get(t, l)
-                sched, cnt = po.pair_schedule(sparse[t, l])
-                assert torch.equal(plan.sched.cpu(), sched) and torch.equal(plan.sched_cnt.cpu(), cnt)
+                # the store pairs q-blocks by overlap: its step counts carry the pairs' q-block ids (+1) in their
+                # high halves, and its lists are the oracle's lists of the mask with the rows in that order
+                words = plan.sched_cnt.cpu()
+                ids = ((words >> 16) & 0xFFFF) - 1
+                m = sparse[t, l]
+                if (ids >= 0).any():
+                    order = ids.view(H, -1)[:, :nb].long()
+                    assert all(sorted(order[h].tolist()) == list(range(nb)) for h in range(H))
+                    m = torch.gather(m, 1, order.unsqueeze(-1).expand(-1, -1, nb))
+                sched, cnt = po.pair_schedule(m)
+                assert torch.equal(plan.sched.cpu(), sched) and torch.equal(words & 0xFFFF, cnt)
                 assert plan.kept_blocks == int(sparse[t, l].sum())
     N, D = nb * 64 - 20, 64
     q, k, v, orders = po.make_inputs(1, H, N, D, torch.float16, seed=4)

@@ -269,3 +269,38 @@ def test_processors_apply_the_embedding_they_are_given_and_prefetch_plans():
     wwant = po.paro_attention(*(t.transpose(1, 2).cpu() for t in (q, k, v)), orders[0].tolist(), wmask, wgrid,
                               rope=("complex", wc, ws))
     assert_close(wout.view(1, wn, heads, D).transpose(1, 2), wwant, "wan processor vs oracle")
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("D,N,H,density,n_text", [(128, 64 * 23 + 17, 3, 0.35, 0), (64, 64 * 16, 2, 0.5, 0),
+                                                   (64, 226 + 4 * 6 * 10, 2, 0.4, 226)])
+def test_pairs_chosen_by_overlap(D, N, H, density, n_text):
+    """compact_plan(pairing="overlap"): every q-block is in exactly one pair, the paired plan needs no more
+    tiles than the adjacent one, and the kernel's output on it equals the adjacent plan's within rounding
+    of the accumulation order (the oracle comparison on such plans: test_kernel_on_oracle_quantised_operands)."""
+    g = torch.Generator().manual_seed(11)
+    nb = (N + 63) // 64
+    mask = po.make_mask(H, nb, density, seed=7, text_blocks=(n_text + 63) // 64)
+    adj = pb.compact_plan(mask.to(DEV))
+    ovl = pb.compact_plan(mask.to(DEV), pairing="overlap", validate=True)
+    assert ovl.pair_tiles <= adj.pair_tiles and ovl.kept_blocks == adj.kept_blocks
+    if ovl.pair_q is not None:
+        pq = ovl.pair_q.view(H, -1).cpu()
+        for h in range(H):
+            ids = pq[h][pq[h] >= 0]
+            assert sorted(ids.tolist()) == list(range(nb))
+    q = torch.randn(1, H, N, D, generator=g).to(torch.bfloat16).to(DEV)
+    k = (torch.randn(1, H, N, D, generator=g) + 1.4 * torch.randn(1, H, 1, D, generator=g)).to(torch.bfloat16).to(DEV)
+    v = torch.randn(1, H, N, D, generator=g).to(torch.bfloat16).to(DEV)
+    q8, qs, k8, ks = pb.per_warp_int8(q, k, pb.channel_mean(k), BLKQ=64, WARPQ=32, BLKK=64)
+    _, vs, vm, v16 = pb.per_channel_fp8(v, return_16=True)
+    outs = {}
+    for name, plan in (("adjacent", adj), ("overlap", ovl)):
+        for mode in ("fast", "exact"):
+            o, lse = pb.sparse_attn_quantized(q8, qs, k8, ks, v16, vs, vm, plan, D ** -0.5, mode=mode, return_lse=True)
+            outs[name, mode] = (o.float().cpu(), lse.cpu())
+    pb.check_status()
+    for mode in ("fast", "exact"):
+        a, b = outs["adjacent", mode], outs["overlap", mode]
+        assert po.cosine_per_head(b[0], a[0]).min().item() > 0.99999
+        assert torch.allclose(b[1], a[1], atol=2e-3, rtol=0)
