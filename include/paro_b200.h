@@ -208,7 +208,8 @@ int paro_plan_schedule(const int32_t* pair_ptr, const int32_t* pair_ent, int sli
  * by other code) before paro_sparse_attn follows them: pair_ptr starts at 0, is monotone and stays within
  * sched_len entries; each q-block's step count fits its pair's slots (and is 0 for a q-block past the end);
  * every k-block id inside a q-block's steps is < nbk and every entry past them is the 0xFFFF filler;
- * shared steps come first and the k-blocks of each section ascend strictly (so none repeats).
+ * shared steps come first and the k-blocks of each section ascend strictly (so none repeats); a q-block id
+ * carried in the high half of a step count is < nbq.
  * report: 4 device words of scratch.  Synchronises `stream`; returns PARO_OK or PARO_EINVAL with the first
  * fault in paro_last_error().  The reference shape-checks its mask argument in the same spirit
  * (csrc/qattn/qk_int_sv_f16_cuda_sm80.cu:1034-1038). */
