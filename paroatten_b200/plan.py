@@ -132,7 +132,7 @@ def compact_plan(mask: torch.Tensor, validate: Optional[bool] = None, pairing: s
     validate: run validate_plan on the result (default: only when the environment variable
     PARO_DEBUG_PLANS is set to a non-empty value other than 0).
     pairing: "adjacent" -- work item p is q-blocks 2p and 2p+1; "overlap" -- q-blocks are paired by the
-    k-blocks they share (pair_rows_by_overlap), kept only if that needs fewer tiles than adjacency."""
+    k-blocks they share (pair_rows_by_overlap), kept for the slices (heads) where that needs fewer tiles than adjacency."""
     if pairing not in ("adjacent", "overlap"):
         raise ValueError(f"unknown pairing {pairing!r}")
     if pairing == "overlap":
@@ -143,11 +143,20 @@ def compact_plan(mask: torch.Tensor, validate: Optional[bool] = None, pairing: s
         base = compact_plan(m0, validate=validate)
         if nbq0 < 4 or nbq0 >= 0xFFFF:
             return base
+        npairs0 = (nbq0 + 1) // 2
         order = pair_rows_by_overlap(m0)
         plan = compact_plan(torch.gather(m0, 1, order.unsqueeze(-1).expand(-1, -1, nbk0)), validate=validate)
-        if plan.pair_tiles >= base.pair_tiles:
+        # The choice is made slice by slice (head by head), so that a head's plan -- and with it the order
+        # in which its rows accumulate -- does not depend on which other heads are compacted with it.
+        ends = torch.arange(0, m0.shape[0] + 1, device=m0.device) * npairs0
+        per_slice = lambda pl: (pl.pair_ptr[ends[1:]] - pl.pair_ptr[ends[:-1]])
+        better = per_slice(plan) < per_slice(base)
+        if not bool(better.any()):
             return base
-        npairs0 = (nbq0 + 1) // 2
+        if not bool(better.all()):
+            ident = torch.arange(nbq0, device=m0.device).expand_as(order)
+            order = torch.where(better.unsqueeze(1), order, ident)
+            plan = compact_plan(torch.gather(m0, 1, order.unsqueeze(-1).expand(-1, -1, nbk0)), validate=validate)
         pq = torch.full((m0.shape[0], 2 * npairs0), -1, dtype=torch.int32, device=m0.device)
         pq[:, :nbq0] = order.to(torch.int32)
         plan.pair_q = pq.view(-1, 2).contiguous()
